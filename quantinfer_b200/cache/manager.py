@@ -100,6 +100,8 @@ class CacheView:
     v_pages: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None   # [num_slots, *shape] for StateNeed entries
     writes: bool = True
+    block_state: Optional[torch.Tensor] = None   # state of fixed size the call's BLOCK keeps beside its mixer (`state_need`)
+    mixer_state: Optional[torch.Tensor] = None   # state of fixed size a mixer keeps BESIDE its pages (`state_need` of a mixer)
 
 
 class CacheManager:

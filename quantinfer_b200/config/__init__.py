@@ -3,10 +3,11 @@ from .registry import (architectures, config_class_for, config_from_dict, load_c
                        register_architecture)
 from .bebuvik import BebuvikConfig
 from .kiruvik import KiruvikConfig
+from .dulotar import DulotarConfig
 from .spec import (AttentionSpec, BigramEmbeddingSpec, DenseFeedForwardSpec, EmbeddingSpec, FeedForwardSpec, HeadSpec,
                    LatentAttentionSpec, LayerCall, LayerSpec, ModelSpec, NormSpec, ParallelLayerSpec, PositionSpec,
                    RotarySpec, ShortConvSpec, ClampedGLUSpec, GatedAttentionSpec, MoESpec, ReentrySpec, SandwichLayerSpec,
-                   StateSpaceSpec)
+                   StateSpaceSpec, ConvPreNormLayerSpec, LightningAttentionSpec, MinGRUSpec, ParallelMixersSpec, TimeMixSpec)
 
 __all__ = [
     "Qwen3Config", "architectures", "config_class_for", "config_from_dict", "load_config",
@@ -14,4 +15,5 @@ __all__ = [
     "LayerCall", "LayerSpec", "ModelSpec", "NormSpec", "PositionSpec", "BebuvikConfig", "BigramEmbeddingSpec",
     "DenseFeedForwardSpec", "LatentAttentionSpec", "ParallelLayerSpec", "RotarySpec", "ShortConvSpec",
     "KiruvikConfig", "ClampedGLUSpec", "GatedAttentionSpec", "MoESpec", "ReentrySpec", "SandwichLayerSpec", "StateSpaceSpec",
+    "DulotarConfig", "ConvPreNormLayerSpec", "LightningAttentionSpec", "MinGRUSpec", "ParallelMixersSpec", "TimeMixSpec",
 ]

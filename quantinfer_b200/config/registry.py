@@ -76,6 +76,9 @@ def _register_builtin() -> None:
     from .kiruvik import ARCHITECTURE as KIRUVIK, KiruvikConfig
 
     register_architecture(KIRUVIK, KiruvikConfig)
+    from .dulotar import ARCHITECTURE as DULOTAR, DulotarConfig
+
+    register_architecture(DULOTAR, DulotarConfig)
 
 
 _register_builtin()

@@ -24,7 +24,8 @@ class NormSpec:
     """`kind` "rmsnorm": gain per coordinate, tensor `prefix + "weight"`. "rmsnorm_scalar": one gain for all
     coordinates, the tensor named `prefix` itself, of shape []. "dyt": dynamic tanh, tanh(alpha x) w + b with no
     statistic of the row (eps unused): w is the tensor named `prefix` itself, b `prefix + ".b"`, alpha
-    `prefix + ".alpha"` of shape []."""
+    `prefix + ".alpha"` of shape []. "layernorm": (x - mean) / sqrt(variance + eps) * w + b with the variance the mean
+    squared deviation; w is the tensor named `prefix` itself, b `prefix + ".b"`."""
 
     size: int
     eps: float
@@ -192,6 +193,83 @@ class GatedAttentionSpec:
     out_gate: bool = True
     prefix: str = ""
     kind: str = "gated_attention"
+    conv_taps: Optional[int] = None    # n: q, k and v each pass a causal convolution of n taps per channel right after their
+                                       # projection (tensors `q.conv`, `k.conv`, `v.conv` [channels, n], no bias); the last
+                                       # n - 1 projected rows are a request's state
+    softcap: Optional[float] = None    # c: a score s becomes c tanh(s / c) before the softmax
+    out_scale: float = 1.0             # a factor on what the mixer hands on (applied before the output projection)
+
+
+@dataclass(frozen=True)
+class MinGRUSpec:
+    """A gated recurrence per channel whose gates read only the current token: z = sigmoid(W_z x + b_z),
+    u = W_x x + b_x, candidate c = u + 1/2 where u >= 0 and sigmoid(u) below; S_t = (1 - z) S_(t-1) + z c;
+    out = W_o (S_t * silu(W_g x)). Tensors `z`, `z.b`, `x`, `x.b`, `g`, `o` after the prefix; S is 32-bit state."""
+
+    hidden_size: int
+    width: int
+    prefix: str = ""
+    kind: str = "mingru"
+
+
+@dataclass(frozen=True)
+class TimeMixSpec:
+    """Time mixing over a matrix state per head with a decay per head and key channel (RWKV style). Each of r, k, v,
+    g, w reads its own mix of the token's input with its predecessor's, x + (x' - x) mu_s (`mu.r` ...); r, k, v are
+    projections of theirs to `heads` x `head_dim`; gate = silu(W_g mix_g); decay = exp(-exp(W_w2 tanh(W_w1 mix_w) +
+    w0)) (`w1` [rank, hidden], `w2` [heads head_dim, rank], `w0`); o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t (`u`
+    [heads, head_dim]); S_t = diag(decay_t) S_(t-1) + k_t v_t^T; every head's o over its root mean square, times
+    `norm`, times the gate, W_o. The state (32-bit) is S and the predecessor's input."""
+
+    hidden_size: int
+    heads: int
+    head_dim: int
+    decay_rank: int
+    norm_eps: float
+    prefix: str = ""
+    kind: str = "time_mix"
+
+
+@dataclass(frozen=True)
+class LightningAttentionSpec:
+    """Linear attention over a matrix state per head with one constant decay a head: q = silu(W_q x), k = silu(W_k x)
+    (`heads` x `head_dim`), v = silu(W_v x) (`heads` x `value_dim`); S_t = decay_h S_(t-1) + k_t v_t^T; o_t = S_t^T q_t;
+    the concatenated heads pass one RMS norm with gain (`norm`), times sigmoid(W_g x), W_o. `out_scale`: a factor on
+    what the mixer hands on (applied before the output projection)."""
+
+    hidden_size: int
+    heads: int
+    head_dim: int
+    value_dim: int
+    decays: tuple
+    norm_eps: float
+    out_scale: float = 1.0
+    prefix: str = ""
+    kind: str = "lightning_attention"
+
+
+@dataclass(frozen=True)
+class ParallelMixersSpec:
+    """Two mixers side by side that read the same input; their outputs are added. Each branch's own factor is a field of
+    its spec (`out_scale`). At most one branch keeps pages; every other state is of fixed size."""
+
+    left: object
+    right: object
+    prefix: str = ""
+    kind: str = "parallel_mixers"
+
+
+@dataclass(frozen=True)
+class ConvPreNormLayerSpec:
+    """The pre-norm block whose mixer reads h + conv(h) instead of h = norm1(x): x += mixer(h + conv(h));
+    x += ffn(norm2(x)). `conv` None: the plain pre-norm block; `ffn` (with its norm) may be None."""
+
+    mixer_norm: NormSpec
+    mixer: object
+    ffn_norm: Optional[NormSpec]
+    ffn: object
+    conv: Optional[ShortConvSpec] = None
+    kind: str = "prenorm_conv"
 
 
 @dataclass(frozen=True)
@@ -301,6 +379,7 @@ class EmbeddingSpec:
     prefix: str = ""
     kind: str = "embedding"
     weight_name: Optional[str] = None   # the tensor's full name when it is not prefix + "weight"
+    scale: float = 1.0                  # the row is multiplied by this (32-bit) on its way into the stream
 
 
 @dataclass(frozen=True)

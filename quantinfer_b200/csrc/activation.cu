@@ -8,18 +8,22 @@
 //   gelu       g * 0.5 * (1 + erf(g / sqrt 2))
 //   gelu_tanh  g * 0.5 * (1 + tanh(sqrt(2 / pi) * (g + 0.044715 g^3)))
 //   relu       max(g, 0)
+//   relu2      max(g, 0)^2
+//   tanh       tanh(g)
 // (the reference's description of a model names Gelu and Relu beside Silu and uses neither,
 // crates/quantinfer-model/src/semantic.rs:26-30). All in 32-bit.
 #include "common.cuh"
 
 namespace {
 
-enum Act : int { kSilu = 0, kGelu = 1, kGeluTanh = 2, kRelu = 3 };
+enum Act : int { kSilu = 0, kGelu = 1, kGeluTanh = 2, kRelu = 3, kRelu2 = 4, kTanh = 5 };
 
 template <int ACT> __device__ __forceinline__ float act(float g) {
     if (ACT == kSilu) return g / (1.0f + expf(-g));
     if (ACT == kGelu) return g * 0.5f * (1.0f + erff(g * 0.70710678118654752f));
     if (ACT == kGeluTanh) return g * 0.5f * (1.0f + tanhf(0.79788456080286536f * (g + 0.044715f * g * g * g)));
+    if (ACT == kRelu2) { const float r = fmaxf(g, 0.f); return r * r; }
+    if (ACT == kTanh) return tanhf(g);
     return fmaxf(g, 0.f);
 }
 
@@ -40,11 +44,11 @@ __global__ void act_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ ou
 
 }  // namespace
 
-// activation: 0 silu, 1 gelu (erf), 2 gelu_tanh, 3 relu.
+// activation: 0 silu, 1 gelu (erf), 2 gelu_tanh, 3 relu, 4 relu squared, 5 tanh.
 extern "C" int qi_act_mul(const void* gate_up, void* out, int dtype, int n_tokens, int inter, int interleaved,
                           int activation, cudaStream_t stream) {
     QI_REQUIRE(n_tokens >= 0 && inter > 0, "act_mul: bad sizes n=%d inter=%d", n_tokens, inter);
-    QI_REQUIRE(activation >= 0 && activation <= 3, "act_mul: unknown activation code %d", activation);
+    QI_REQUIRE(activation >= 0 && activation <= 5, "act_mul: unknown activation code %d", activation);
     if (n_tokens == 0) return 0;
     const size_t total = (size_t)n_tokens * inter;
     size_t blocks = (total + 255) / 256;
@@ -57,6 +61,8 @@ extern "C" int qi_act_mul(const void* gate_up, void* out, int dtype, int n_token
             case kSilu: qi::launch(act_mul_kernel<T, kSilu>, grid, block, 0, stream, in, o, n_tokens, inter, interleaved); break;
             case kGelu: qi::launch(act_mul_kernel<T, kGelu>, grid, block, 0, stream, in, o, n_tokens, inter, interleaved); break;
             case kGeluTanh: qi::launch(act_mul_kernel<T, kGeluTanh>, grid, block, 0, stream, in, o, n_tokens, inter, interleaved); break;
+            case kRelu2: qi::launch(act_mul_kernel<T, kRelu2>, grid, block, 0, stream, in, o, n_tokens, inter, interleaved); break;
+            case kTanh: qi::launch(act_mul_kernel<T, kTanh>, grid, block, 0, stream, in, o, n_tokens, inter, interleaved); break;
             default: qi::launch(act_mul_kernel<T, kRelu>, grid, block, 0, stream, in, o, n_tokens, inter, interleaved); break;
         }
     });
@@ -111,7 +117,7 @@ unsigned blocks_for(size_t total) {
 // out = act(in), elementwise, both [n] in `dtype`; 32-bit arithmetic.
 extern "C" int qi_activation(const void* in, void* out, int dtype, long long n, int activation, cudaStream_t stream) {
     QI_REQUIRE(n >= 0, "activation: bad size");
-    QI_REQUIRE(activation >= 0 && activation <= 3, "activation: unknown activation code %d", activation);
+    QI_REQUIRE(activation >= 0 && activation <= 5, "activation: unknown activation code %d", activation);
     if (n == 0) return 0;
     const dim3 grid(blocks_for((size_t)n)), block(256);
     QI_DISPATCH_DTYPE(dtype, T, {
@@ -119,6 +125,8 @@ extern "C" int qi_activation(const void* in, void* out, int dtype, long long n, 
             case kSilu: qi::launch(activation_kernel<T, kSilu>, grid, block, 0, stream, (const T*)in, (T*)out, (size_t)n); break;
             case kGelu: qi::launch(activation_kernel<T, kGelu>, grid, block, 0, stream, (const T*)in, (T*)out, (size_t)n); break;
             case kGeluTanh: qi::launch(activation_kernel<T, kGeluTanh>, grid, block, 0, stream, (const T*)in, (T*)out, (size_t)n); break;
+            case kRelu2: qi::launch(activation_kernel<T, kRelu2>, grid, block, 0, stream, (const T*)in, (T*)out, (size_t)n); break;
+            case kTanh: qi::launch(activation_kernel<T, kTanh>, grid, block, 0, stream, (const T*)in, (T*)out, (size_t)n); break;
             default: qi::launch(activation_kernel<T, kRelu>, grid, block, 0, stream, (const T*)in, (T*)out, (size_t)n); break;
         }
     });

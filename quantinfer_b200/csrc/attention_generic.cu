@@ -8,7 +8,8 @@
 //     out     = sum_j softmax(score)_j * v_j
 // with lo = 0, or p - window + 1 for a windowed layer, or the start of p's chunk
 // (floor(p / chunk) * chunk, chunks counted from the sequence's first position)
-// for a chunked layer; both bounds may hold at once. Values may have another
+// for a chunked layer; both bounds may hold at once. A soft cap c replaces each
+// score by c tanh(score / c) before the softmax. Values may have another
 // size `dv` than queries and keys, and the result may be multiplied, element by
 // element, by the sigmoid of a gate row (an output gate computed from the
 // mixer's input). Scores, the maximum,
@@ -35,7 +36,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
                          const T* __restrict__ v_pages, const int* __restrict__ block_table,
                          int max_blocks, int page_size, int num_pages,
                          const int* __restrict__ positions, const int* __restrict__ token_req,
-                         int nq, int nkv, int d, int dv, float scale, int window, int chunk,
+                         int nq, int nkv, int d, int dv, float scale, float softcap, float out_scale, int window, int chunk,
                          const T* __restrict__ gate, long long ldg, int* __restrict__ status) {
     extern __shared__ float smem[];
     float* q_s = smem;                          // [d]
@@ -76,6 +77,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
                 float dot = 0.f;
                 for (int i = 0; i < d; ++i) dot = fmaf(q_s[i], qi::to_f32<T>(krow[i]), dot);
                 s = dot * scale;
+                if (softcap > 0.f) s = softcap * tanhf(s / softcap);
             }
         }
         const float cm = qi::warp_max(s);
@@ -129,6 +131,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
         for (int w = 0; w < kWarps; ++w) o += part_acc[w * dv + i] * wscale[w];
         o = gl > 0.f ? o / gl : 0.f;
         if (grow) o = o / (1.0f + expf(-qi::to_f32<T>(grow[i])));
+        o *= out_scale;
         orow[i] = qi::from_f32<T>(o);
     }
 }
@@ -136,18 +139,20 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
 }  // namespace
 
 // q [n, nq d]; out [n, nq dv]; k_pages [pages, nkv, page_size, d]; v_pages [pages, nkv, page_size, dv];
-// window 0: no window; chunk 0: no chunks; gate (may be null): row t, head h, element i at gate[t * ldg + h * dv + i].
-extern "C" int qi_attention_generic_ex(const void* q, void* out, int dtype, const void* k_pages,
+// window 0: no window; chunk 0: no chunks; gate (may be null): row t, head h, element i at gate[t * ldg + h * dv + i];
+// softcap c > 0: a score s becomes c tanh(s / c) before the softmax (0: scores as they are); out_scale multiplies the result.
+extern "C" int qi_attention_generic_cap(const void* q, void* out, int dtype, const void* k_pages,
                                        const void* v_pages, const int* block_table, int max_blocks,
                                        int page_size, int num_pages, const int* positions,
                                        const int* token_req, int n_tokens, int nq, int nkv, int d, int dv,
-                                       float scale, int window, int chunk, const void* gate, long long ldg,
-                                       int* status, cudaStream_t stream) {
+                                       float scale, float softcap, float out_scale, int window, int chunk, const void* gate,
+                                       long long ldg, int* status, cudaStream_t stream) {
     QI_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0 && dv > 0, "attention: bad sizes");
     QI_REQUIRE(nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
     QI_REQUIRE(d <= kMaxD && dv <= kMaxD, "attention: head sizes %d / %d are above the limit %d of this kernel", d, dv, kMaxD);
     QI_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0, "attention: bad page geometry");
     QI_REQUIRE(window >= 0 && chunk >= 0, "attention: window and chunk must be >= 0 (0 = none)");
+    QI_REQUIRE(softcap >= 0.f, "attention: the soft cap must be >= 0 (0 = none)");
     QI_REQUIRE(!gate || ldg >= (long long)nq * dv, "attention: the gate's rows are too short");
     QI_REQUIRE(n_tokens <= 65535 * 32768 && nq <= 65535, "attention: grid too large");
     if (n_tokens == 0) return 0;
@@ -160,11 +165,21 @@ extern "C" int qi_attention_generic_ex(const void* q, void* out, int dtype, cons
             qi::launch(attention_generic_kernel<T>, grid, dim3(kWarps * 32), smem, stream,
                 (const T*)q + (size_t)t0 * nq * d, (T*)out + (size_t)t0 * nq * dv, (const T*)k_pages,
                 (const T*)v_pages, block_table, max_blocks, page_size, num_pages, positions + t0,
-                token_req + t0, nq, nkv, d, dv, scale, window, chunk,
+                token_req + t0, nq, nkv, d, dv, scale, softcap, out_scale, window, chunk,
                 gate ? (const T*)gate + (size_t)t0 * ldg : (const T*)nullptr, ldg, status);
         });
     }
     return qi::check_launch("attention_generic");
+}
+
+extern "C" int qi_attention_generic_ex(const void* q, void* out, int dtype, const void* k_pages,
+                                       const void* v_pages, const int* block_table, int max_blocks,
+                                       int page_size, int num_pages, const int* positions,
+                                       const int* token_req, int n_tokens, int nq, int nkv, int d, int dv,
+                                       float scale, int window, int chunk, const void* gate, long long ldg,
+                                       int* status, cudaStream_t stream) {
+    return qi_attention_generic_cap(q, out, dtype, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, positions,
+                                    token_req, n_tokens, nq, nkv, d, dv, scale, 0.f, 1.f, window, chunk, gate, ldg, status, stream);
 }
 
 extern "C" int qi_attention_generic(const void* q, void* out, int dtype, const void* k_pages,

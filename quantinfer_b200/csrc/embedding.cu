@@ -10,7 +10,7 @@ namespace {
 
 template <typename TW>
 __global__ void embedding_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, int hidden, int vocab,
+                                 float* __restrict__ out, int hidden, int vocab, float scale,
                                  int* __restrict__ status) {
     qi::pdl_enter();
     const int t = blockIdx.x;
@@ -22,23 +22,30 @@ __global__ void embedding_kernel(const TW* __restrict__ table, const int* __rest
         return;
     }
     const TW* src = table + (size_t)id * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = qi::to_f32<TW>(src[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = qi::to_f32<TW>(src[i]) * scale;
 }
 
 }  // namespace
 
-extern "C" int qi_embedding(const void* table, int table_dtype, const int* ids, float* out,
-                            int n_tokens, int hidden, int vocab, int* status,
-                            cudaStream_t stream) {
+// residual[t, :] = table[ids[t], :] * scale (the product in 32-bit).
+extern "C" int qi_embedding_scaled(const void* table, int table_dtype, const int* ids, float* out,
+                                   int n_tokens, int hidden, int vocab, float scale, int* status,
+                                   cudaStream_t stream) {
     QI_REQUIRE(n_tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes n=%d hidden=%d vocab=%d",
                n_tokens, hidden, vocab);
     if (n_tokens == 0) return 0;
     const int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
     QI_DISPATCH_DTYPE(table_dtype, TW, {
         qi::launch(embedding_kernel<TW>, dim3(n_tokens), dim3(threads), 0, stream, (const TW*)table, ids, out, hidden, vocab,
-                   status);
+                   scale, status);
     });
     return qi::check_launch("embedding");
+}
+
+extern "C" int qi_embedding(const void* table, int table_dtype, const int* ids, float* out,
+                            int n_tokens, int hidden, int vocab, int* status,
+                            cudaStream_t stream) {
+    return qi_embedding_scaled(table, table_dtype, ids, out, n_tokens, hidden, vocab, 1.0f, status, stream);
 }
 
 // Embedding with a hashed bigram table added: residual[t, :] = table[id_t, :] + bigram[row_t, :], where

@@ -3,8 +3,8 @@
 // visibility may be bounded by a chunk and a window besides causality, and whose result may pass an
 // output gate:
 //
-//     s_ij = (q_i . k_j) * scale    for lo(i) <= j <= i,   lo(i) = max(start of i's chunk, i - window + 1, 0)
-//     out_i = (sum_j softmax(s_i)_j v_j) * sigmoid(gate_i)
+//     s_ij = cap((q_i . k_j) * scale)    for lo(i) <= j <= i,   lo(i) = max(start of i's chunk, i - window + 1, 0)
+//     out_i = (sum_j softmax(s_i)_j v_j) * sigmoid(gate_i) * out_scale      cap(s) = c tanh(s / c), or s without a cap
 //
 // One kernel serves prompts, portions and single decode tokens: a CTA of four warps takes up to 64
 // consecutive query rows of ONE step entry and one query head (the tiles are found on the device from
@@ -71,8 +71,8 @@ __global__ void __launch_bounds__(kThreads)
 gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict__ out, const qi::bf16* __restrict__ k_pages,
                            const qi::bf16* __restrict__ v_pages, const int* __restrict__ block_table, int max_blocks,
                            int page_size, int num_pages, const int* __restrict__ q_start, const int* __restrict__ start_pos,
-                           int n_entries, int nq, int nkv, int d, int dv, float scale_log2e, int window, int chunk,
-                           const qi::bf16* __restrict__ gate, long long ldg, int* __restrict__ status) {
+                           int n_entries, int nq, int nkv, int d, int dv, float scale_log2e, float softcap, float out_scale,
+                           int window, int chunk, const qi::bf16* __restrict__ gate, long long ldg, int* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     constexpr int SK = DK + kPad, SV = DV + kPad;
     qi::bf16* Qs = reinterpret_cast<qi::bf16*>(smem_raw);       // [kQT][SK]
@@ -168,6 +168,15 @@ gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict_
             for (int kk = 0; kk < DK / 16; ++kk)
                 mma_bf16(s[n], qa[kk], *reinterpret_cast<const uint32_t*>(kr + kk * 16), *reinterpret_cast<const uint32_t*>(kr + kk * 16 + 8));
         }
+        // soft cap: c tanh(s scale / c), then into the base-2 exponent like the plain scale
+        if (softcap > 0.f) {
+            const float a = scale_log2e * (0.6931471805599453f / softcap), b = softcap * 1.4426950408889634f / scale_log2e;
+#pragma unroll
+            for (int n = 0; n < kKT / 8; ++n) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) s[n][j] = b * tanhf(s[n][j] * a);
+            }
+        }
         // mask, scale (into the base-2 exponent), row maxima
         float tmA = -INFINITY, tmB = -INFINITY;
 #pragma unroll
@@ -223,7 +232,7 @@ gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict_
     if (bad_page && status) atomicOr(status, qi::kStatusBadPage);
     lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
     lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
-    const float iA = lA > 0.f ? 1.0f / lA : 0.f, iB = lB > 0.f ? 1.0f / lB : 0.f;
+    const float iA = lA > 0.f ? 1.0f / lA : 0.f, iB = lB > 0.f ? 1.0f / lB : 0.f;   // out_scale joins below, after the gate
 #pragma unroll
     for (int n = 0; n < DV / 8; ++n) {
         const int col = n * 8 + (lane & 3) * 2;
@@ -239,7 +248,7 @@ gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict_
                 v0 = v0 / (1.0f + expf(-__bfloat162float(g[0])));
                 v1 = v1 / (1.0f + expf(-__bfloat162float(g[1])));
             }
-            *reinterpret_cast<__nv_bfloat162*>(out + (t * nq + h) * dv + col) = __floats2bfloat162_rn(v0, v1);
+            *reinterpret_cast<__nv_bfloat162*>(out + (t * nq + h) * dv + col) = __floats2bfloat162_rn(v0 * out_scale, v1 * out_scale);
         }
     }
 }
@@ -249,8 +258,8 @@ int padded(int v) { return v <= 32 ? 32 : v <= 64 ? 64 : v <= 96 ? 96 : 128; }
 template <int DK, int DV>
 int launch_one(dim3 grid, cudaStream_t stream, const void* q, void* out, const void* k_pages, const void* v_pages,
                const int* block_table, int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
-               int n_entries, int nq, int nkv, int d, int dv, float scale_log2e, int window, int chunk, const void* gate,
-               long long ldg, int* status) {
+               int n_entries, int nq, int nkv, int d, int dv, float scale_log2e, float softcap, float out_scale, int window, int chunk,
+               const void* gate, long long ldg, int* status) {
     const size_t smem = sizeof(qi::bf16) * ((size_t)(kQT + 2 * kKT) * (DK + kPad) + (size_t)2 * kKT * (DV + kPad));
     static bool raised = false;
     if (!raised && smem > 48 * 1024) {
@@ -259,7 +268,7 @@ int launch_one(dim3 grid, cudaStream_t stream, const void* q, void* out, const v
     }
     qi::launch(gated_attention_mma_kernel<DK, DV>, grid, dim3(kThreads), smem, stream, (const qi::bf16*)q, (qi::bf16*)out,
                (const qi::bf16*)k_pages, (const qi::bf16*)v_pages, block_table, max_blocks, page_size, num_pages, q_start, start_pos,
-               n_entries, nq, nkv, d, dv, scale_log2e, window, chunk, (const qi::bf16*)gate, ldg, status);
+               n_entries, nq, nkv, d, dv, scale_log2e, softcap, out_scale, window, chunk, (const qi::bf16*)gate, ldg, status);
     return qi::check_launch("gated_attention_mma");
 }
 
@@ -270,14 +279,16 @@ extern "C" int qi_gated_attention_mma_supported(int nq, int nkv, int d, int dv) 
 }
 
 // q [n, nq d], out [n, nq dv], pages [num_pages, nkv, page_size, d | dv], all bfloat16; q_start [entries + 1],
-// start_pos [entries]; gate (may be null) row t, head h, element i at gate[t * ldg + h * dv + i] (ldg and dv even).
+// start_pos [entries]; gate (may be null) row t, head h, element i at gate[t * ldg + h * dv + i] (ldg and dv even);
+// softcap c > 0: a score s becomes c tanh(s / c) before the softmax; out_scale multiplies the result.
 extern "C" int qi_gated_attention_mma(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
                                       int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
-                                      int n_entries, int n_tokens, int nq, int nkv, int d, int dv, float scale, int window,
-                                      int chunk, const void* gate, long long ldg, int* status, cudaStream_t stream) {
+                                      int n_entries, int n_tokens, int nq, int nkv, int d, int dv, float scale, float softcap,
+                                      float out_scale, int window, int chunk, const void* gate, long long ldg, int* status, cudaStream_t stream) {
     QI_REQUIRE(qi_gated_attention_mma_supported(nq, nkv, d, dv), "gated_attention_mma: heads %d/%d of %d/%d are not covered", nq, nkv, d, dv);
     QI_REQUIRE(n_entries >= 0 && n_tokens >= 0 && page_size > 0 && max_blocks > 0 && num_pages > 0, "gated_attention_mma: bad sizes");
     QI_REQUIRE(window >= 0 && chunk >= 0, "gated_attention_mma: window and chunk must be >= 0 (0 = none)");
+    QI_REQUIRE(softcap >= 0.f && scale > 0.f, "gated_attention_mma: the soft cap must be >= 0 (0 = none) and the scale positive");
     QI_REQUIRE(!gate || (ldg >= (long long)nq * dv && ldg % 2 == 0), "gated_attention_mma: the gate's rows are too short or odd");
     QI_REQUIRE(nq <= 65535, "gated_attention_mma: too many heads");
     if (n_tokens == 0 || n_entries == 0) return 0;
@@ -285,7 +296,7 @@ extern "C" int qi_gated_attention_mma(const void* q, void* out, const void* k_pa
     const float sl = scale * 1.4426950408889634f;
 #define QI_GA(DKP, DVP)                                                                                                      \
     return launch_one<DKP, DVP>(grid, stream, q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start, \
-                                start_pos, n_entries, nq, nkv, d, dv, sl, window, chunk, gate, ldg, status)
+                                start_pos, n_entries, nq, nkv, d, dv, sl, softcap, out_scale, window, chunk, gate, ldg, status)
 #define QI_GA_ROW(DKP)                                   \
     switch (padded(dv)) {                                \
         case 32: QI_GA(DKP, 32);                         \

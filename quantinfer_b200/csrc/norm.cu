@@ -285,6 +285,43 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const float* __restrict_
         orow[i] = qi::from_f32<T>(qi::to_f32<T>(xr[i]) * inv * gain[i]);
 }
 
+// Fused residual add + layer norm with gain and bias:
+//     x = resid[s, :] + sum_k delta[k, s, :] ; out[r, :] = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * gain + bias
+// The mean is taken first and the variance from the deviations (two sums over the row, both 32-bit).
+template <typename TD, typename TO>
+__global__ void add_layernorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, int delta_splits,
+                                     size_t delta_split_stride, const float* __restrict__ gain, const float* __restrict__ bias,
+                                     float eps, TO* __restrict__ out, const int* __restrict__ rows, int hidden, int write_resid) {
+    __shared__ float scratch[32];
+    qi::pdl_wait();
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float* xr = resid + (size_t)s * hidden;
+    const TD* dr = delta ? delta + (size_t)s * hidden : nullptr;
+    auto value = [&](int i) {
+        float x = xr[i];
+        if (dr) {
+            for (int k = 0; k < delta_splits; ++k) x += qi::to_f32<TD>(dr[k * delta_split_stride + i]);
+        }
+        return x;
+    };
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) sum += value(i);
+    const float mean = qi::block_sum(sum, scratch) / (float)hidden;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float d = value(i) - mean;
+        sq = fmaf(d, d, sq);
+    }
+    const float inv = 1.0f / sqrtf(qi::block_sum(sq, scratch) / (float)hidden + eps);
+    TO* orow = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float x = value(i);
+        if (write_resid) xr[i] = x;       // the same thread read it; nobody else reads this element
+        orow[i] = qi::from_f32<TO>(fmaf((x - mean) * inv, gain[i], bias ? bias[i] : 0.f));
+    }
+}
+
 int pick_threads(int hidden) { return hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : (hidden >= 128 ? 128 : 32)); }
 
 }  // namespace
@@ -342,6 +379,27 @@ extern "C" int qi_add_rmsnorm(float* resid, const void* delta, int delta_dtype, 
         });
     });
     return qi::check_launch("add_rmsnorm");
+}
+
+// As qi_add_rmsnorm for a layer norm with gain and bias (bias may be null); out may be float32 or the activation type.
+extern "C" int qi_add_layernorm(float* resid, const void* delta, int delta_dtype, int delta_splits,
+                                long long delta_split_stride, const float* gain, const float* bias, float eps,
+                                void* out, int out_dtype, const int* rows, int n_rows, int hidden,
+                                int write_resid, cudaStream_t stream) {
+    QI_REQUIRE(n_rows >= 0 && hidden > 0, "add_layernorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
+    QI_REQUIRE(!(rows && write_resid), "add_layernorm: the row-gather form does not write the residual");
+    QI_REQUIRE(delta_splits >= 1, "add_layernorm: delta_splits must be >= 1");
+    QI_REQUIRE(eps > 0.f, "add_layernorm: eps must be positive");
+    if (n_rows == 0) return 0;
+    const int dd = delta ? delta_dtype : qi::kF32;
+    const int threads = pick_threads(hidden);
+    QI_DISPATCH_DTYPE(dd, TD, {
+        QI_DISPATCH_DTYPE(out_dtype, TO, {
+            qi::launch(add_layernorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream, resid, (const TD*)delta,
+                       delta_splits, (size_t)delta_split_stride, gain, bias, eps, (TO*)out, rows, hidden, write_resid);
+        });
+    });
+    return qi::check_launch("add_layernorm");
 }
 
 extern "C" int qi_rmsnorm(const void* x, const float* gain, float eps, void* out, int dtype,

@@ -449,10 +449,12 @@ ssm_chain_kernel(float* __restrict__ seg_state, float* __restrict__ state, long 
     }
 }
 
+// mode 0: norm(y * silu(z)) * gain (the gate before the norm); mode 1: norm(y) * gain * silu(z); mode 2: norm(y) * gain *
+// sigmoid(z); mode 3: norm(y) * gain * z (a gate that carries its activation already); all times out_scale.
 template <typename TZ, typename TO>
 __global__ void __launch_bounds__(256)
 gated_group_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, long long ldz, const float* __restrict__ gain,
-                           float eps, TO* __restrict__ out, int width, int groups) {
+                           float eps, TO* __restrict__ out, int width, int groups, int mode, float out_scale) {
     __shared__ float scratch[32];
     qi::pdl_wait();
     const int t = blockIdx.x, grp = blockIdx.y;
@@ -461,16 +463,25 @@ gated_group_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z
     const TZ* zr = z + (size_t)t * ldz + (size_t)grp * gw;
     float ss = 0.f;
     for (int i = threadIdx.x; i < gw; i += blockDim.x) {
-        const float zz = qi::to_f32<TZ>(zr[i]);
-        const float v = yr[i] * (zz / (1.0f + expf(-zz)));
+        float v = yr[i];
+        if (mode == 0) {
+            const float zz = qi::to_f32<TZ>(zr[i]);
+            v *= zz / (1.0f + expf(-zz));
+        }
         ss = fmaf(v, v, ss);
     }
     const float total = qi::block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(total / (float)gw + eps);
     for (int i = threadIdx.x; i < gw; i += blockDim.x) {
         const float zz = qi::to_f32<TZ>(zr[i]);
-        const float v = yr[i] * (zz / (1.0f + expf(-zz)));
-        out[(size_t)t * width + (size_t)grp * gw + i] = qi::from_f32<TO>(v * inv * gain[(size_t)grp * gw + i]);
+        const float sg = 1.0f / (1.0f + expf(-zz));
+        float v = yr[i];
+        if (mode == 0) v *= zz * sg;
+        v = v * inv * gain[(size_t)grp * gw + i];
+        if (mode == 1) v *= zz * sg;
+        else if (mode == 2) v *= sg;
+        else if (mode == 3) v *= zz;
+        out[(size_t)t * width + (size_t)grp * gw + i] = qi::from_f32<TO>(v * out_scale);
     }
 }
 
@@ -575,16 +586,24 @@ extern "C" int qi_ssm_chain(float* seg_state, float* state, long long state_stri
 }
 
 // y float32 [n, width]; z [n, >= width] in z_dtype with `ldz` elements a row; gain float32 [width]; out [n, width] in out_dtype.
-extern "C" int qi_gated_group_rmsnorm(const float* y, const void* z, int z_dtype, long long ldz, const float* gain, float eps,
-                                      void* out, int out_dtype, int n, int width, int groups, cudaStream_t stream) {
+// mode 0: rmsnorm_groups(y * silu(z)) * gain; 1: rmsnorm_groups(y) * gain * silu(z); 2: ... * sigmoid(z); 3: ... * z.
+extern "C" int qi_group_rmsnorm_gate(const float* y, const void* z, int z_dtype, long long ldz, const float* gain, float eps,
+                                     void* out, int out_dtype, int n, int width, int groups, int mode, float out_scale,
+                                     cudaStream_t stream) {
     QI_REQUIRE(n >= 0 && width > 0 && groups > 0 && width % groups == 0, "gated_group_rmsnorm: bad sizes n=%d width=%d groups=%d", n, width, groups);
     QI_REQUIRE(ldz >= width && groups <= 65535, "gated_group_rmsnorm: bad layout");
+    QI_REQUIRE(mode >= 0 && mode <= 3, "gated_group_rmsnorm: unknown mode %d", mode);
     if (n == 0) return 0;
     QI_DISPATCH_DTYPE(z_dtype, TZ, {
         QI_DISPATCH_DTYPE(out_dtype, TO, {
             qi::launch(gated_group_rmsnorm_kernel<TZ, TO>, dim3(n, groups), dim3(256), 0, stream, y, (const TZ*)z, ldz, gain, eps,
-                       (TO*)out, width, groups);
+                       (TO*)out, width, groups, mode, out_scale);
         });
     });
     return qi::check_launch("gated_group_rmsnorm");
+}
+
+extern "C" int qi_gated_group_rmsnorm(const float* y, const void* z, int z_dtype, long long ldz, const float* gain, float eps,
+                                      void* out, int out_dtype, int n, int width, int groups, cudaStream_t stream) {
+    return qi_group_rmsnorm_gate(y, z, z_dtype, ldz, gain, eps, out, out_dtype, n, width, groups, 0, 1.0f, stream);
 }

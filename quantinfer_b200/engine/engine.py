@@ -86,9 +86,11 @@ class Engine:
         self.cache = CacheManager(self.model.cache_needs, page_size, num_pages, max_requests,
                                   self.max_seq_len, self.dtype, self.device)
         self._views = [self.cache.view(call.cache, call.writes_cache) for call in self.model.order]
-        for view, entry in zip(self._views, self.model.call_state_entry):
+        for view, entry, mixer_entry in zip(self._views, self.model.call_state_entry, self.model.call_mixer_state_entry):
             if entry is not None:
-                view.state = self.cache.states[entry]      # the call's own state of fixed size, beside its pages
+                view.block_state = self.cache.states[entry]      # the block's own state of fixed size
+            if mixer_entry is not None:
+                view.mixer_state = self.cache.states[mixer_entry]  # the mixer's, beside its pages
         if self.model.embedding_state_entry is not None:
             self.model.embedding_view = self.cache.view(self.model.embedding_state_entry)
         from ..sampling.slots import RequestSlots

@@ -63,12 +63,15 @@ class Model:
                 self.cache_needs[call.cache] = merged
         # state of fixed size that parts keep besides the mixers' entries: one more entry per layer call whose
         # block asks for it (`state_need`), and one for the embedding; the engine hands each its view
-        self.call_state_entry = []
+        # and one more for a mixer that keeps such state BESIDE its pages (the block passes its mixer's `state_need` on
+        # as `mixer_state_need`)
+        self.call_state_entry, self.call_mixer_state_entry = [], []
         for call in self.order:
-            need = getattr(self.blocks[call.layer], "state_need", lambda: None)()
-            self.call_state_entry.append(len(self.cache_needs) if need is not None else None)
-            if need is not None:
-                self.cache_needs.append(need)
+            for name, entries in (("state_need", self.call_state_entry), ("mixer_state_need", self.call_mixer_state_entry)):
+                need = getattr(self.blocks[call.layer], name, lambda: None)()
+                entries.append(len(self.cache_needs) if need is not None else None)
+                if need is not None:
+                    self.cache_needs.append(need)
         need = getattr(self.embedding, "state_need", lambda: None)()
         self.embedding_state_entry = len(self.cache_needs) if need is not None else None
         if need is not None:

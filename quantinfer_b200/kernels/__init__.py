@@ -25,7 +25,7 @@ STATUS_NON_FINITE = 4
 STATUS_WAIT_TIMEOUT = 8
 STATUS_BAD_RANGE = 16
 
-ABI_VERSION = 11
+ABI_VERSION = 12
 
 
 def status_names(code: int) -> list:
@@ -147,8 +147,8 @@ def _ptr(t) -> C.c_void_p:
 # embedding
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
-    """out[t, :] = table[ids[t], :] as float32. ids int32 [n]; out float32 [n, hidden]."""
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t, :] = table[ids[t], :] * scale as float32. ids int32 [n]; out float32 [n, hidden]."""
     _req(table, "table", ndim=2)
     _req(ids, "ids", torch.int32, 1)
     _req(out, "out", torch.float32, 2)
@@ -156,9 +156,9 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status:
     n, hidden = out.shape
     if ids.numel() != n or table.shape[1] != hidden:
         raise KernelError(f"embedding: shapes do not agree: table {tuple(table.shape)}, ids {tuple(ids.shape)}, out {tuple(out.shape)}")
-    _call('other', "embedding", library().qi_embedding,
+    _call('other', "embedding", library().qi_embedding_scaled,
           _ptr(table), _code(table), _ptr(ids), _ptr(out), n, hidden,
-                                table.shape[0], _ptr(status), _stream())
+                                table.shape[0], C.c_float(scale), _ptr(status), _stream())
 
 
 # --------------------------------------------------------------------------
@@ -199,6 +199,37 @@ def add_rmsnorm(resid: torch.Tensor, delta, gain: torch.Tensor, eps: float, out:
           _ptr(resid), _ptr(delta), _code(delta) if delta is not None else F32, splits,
         C.c_longlong(stride), _ptr(gain), C.c_float(eps), _ptr(out), _code(out), _ptr(rows), n_out, h,
         int(bool(write_resid)), _stream())
+
+
+def add_layernorm(resid: torch.Tensor, delta, gain: torch.Tensor, bias, eps: float, out: torch.Tensor,
+                  rows=None, write_resid: bool = True) -> None:
+    """Fused residual add and layer norm: x = resid + delta; out = (x - mean) / sqrt(var + eps) * gain + bias, var the
+    mean squared deviation. Arguments as for `add_rmsnorm`; bias float32 [h] or None; out float32 or the activation type."""
+    _req(resid, "resid", torch.float32, 2)
+    _req(gain, "gain", torch.float32, 1)
+    _req(out, "out", ndim=2)
+    n, h = resid.shape
+    splits, stride = 1, 0
+    if delta is not None:
+        _req(delta, "delta")
+        if delta.dim() == 3:
+            splits, stride = delta.shape[0], delta.shape[1] * delta.shape[2]
+        if tuple(delta.shape[-2:]) != (n, h):
+            raise KernelError(f"add_layernorm: delta {tuple(delta.shape)} does not match resid {tuple(resid.shape)}")
+    if bias is not None:
+        _req(bias, "bias", torch.float32, 1)
+    if gain.numel() != h or (bias is not None and bias.numel() != h):
+        raise KernelError(f"add_layernorm: gain and bias must have {h} elements")
+    n_out = n
+    if rows is not None:
+        _req(rows, "rows", torch.int32, 1)
+        n_out = rows.numel()
+        write_resid = False
+    if tuple(out.shape) != (n_out, h):
+        raise KernelError(f"add_layernorm: out is {tuple(out.shape)}, expected {(n_out, h)}")
+    _call('norm', "add_layernorm", library().qi_add_layernorm,
+          _ptr(resid), _ptr(delta), _code(delta) if delta is not None else F32, splits, C.c_longlong(stride), _ptr(gain),
+          _ptr(bias), C.c_float(eps), _ptr(out), _code(out), _ptr(rows), n_out, h, int(bool(write_resid)), _stream())
 
 
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor) -> None:
@@ -304,11 +335,13 @@ def qk_norm_rope_kv(qkv, q_out, q_gain, k_gain, eps, cos, sin, rotary_dim, posit
 
 
 def attention_generic(q, out, k_pages, v_pages, block_table, positions, token_req, nq, nkv, d,
-                      scale: float, window: int, status, chunk: int = 0, gate=None) -> None:
+                      scale: float, window: int, status, chunk: int = 0, gate=None, softcap: float = 0.0,
+                      out_scale: float = 1.0) -> None:
     """Causal paged GQA attention, 32-bit arithmetic, any span length and page size. Values may have another
     size than keys (v_pages [pages, nkv, page_size, dv], out [n, nq dv]); `chunk` > 0: a query sees only the keys
     of its own chunk of that many positions (counted from the sequence's start); `gate` [n, >= nq dv] (a view whose
-    rows may lie further apart): the result is multiplied by sigmoid(gate)."""
+    rows may lie further apart): the result is multiplied by sigmoid(gate). `softcap` c > 0: a score s becomes
+    c tanh(s / c) before the softmax. `out_scale` multiplies the result."""
     _req(q, "q", ndim=2)
     _req(out, "out", q.dtype, 2)
     _req(k_pages, "k_pages", q.dtype, 4)
@@ -327,10 +360,10 @@ def attention_generic(q, out, k_pages, v_pages, block_table, positions, token_re
         if not gate.is_cuda or gate.dtype != q.dtype or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != out.shape:
             raise KernelError("attention: the gate must be [n, nq dv] in q's type with contiguous rows")
         ldg = gate.stride(0)
-    _call('attention', "attention_generic", library().qi_attention_generic_ex,
+    _call('attention', "attention_generic", library().qi_attention_generic_cap,
           _ptr(q), _ptr(out), _code(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
         block_table.shape[1], k_pages.shape[2], k_pages.shape[0], _ptr(positions), _ptr(token_req), n,
-        nq, nkv, d, dv, C.c_float(scale), int(window or 0), int(chunk or 0), _ptr(gate), C.c_longlong(ldg), _ptr(status), _stream())
+        nq, nkv, d, dv, C.c_float(scale), C.c_float(softcap or 0.0), C.c_float(out_scale), int(window or 0), int(chunk or 0), _ptr(gate), C.c_longlong(ldg), _ptr(status), _stream())
 
 
 def attention_mma_supported(nq: int, nkv: int, d: int) -> bool:
@@ -548,7 +581,7 @@ def attention_decode_rope(qkv, out, q_gain, k_gain, eps, cos, sin, k_pages, v_pa
 # feed-forward
 
 
-ACTIVATIONS = {"silu": 0, "gelu": 1, "gelu_tanh": 2, "relu": 3}
+ACTIVATIONS = {"silu": 0, "gelu": 1, "gelu_tanh": 2, "relu": 3, "relu2": 4, "tanh": 5}
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
@@ -1152,9 +1185,16 @@ def ssm_chain(seg_state, state, raw_dt, dt_bias, a_log, seg_q_start, entry_seg, 
           _ptr(start_pos), _ptr(slot_ids), start_pos.numel(), int(max_segments), heads, P, N, _stream())
 
 
-def gated_group_rmsnorm(y, z, gain, eps: float, out, groups: int) -> None:
-    """out = rmsnorm_groups(y * silu(z)) * gain: every width / groups coordinates by their own root mean square.
+GATE_MODES = {"silu_before": 0, "silu": 1, "sigmoid": 2, "plain": 3}
+
+
+def gated_group_rmsnorm(y, z, gain, eps: float, out, groups: int, gate: str = "silu_before", out_scale: float = 1.0) -> None:
+    """Every width / groups coordinates of a row by their own root mean square, a gain, and a gate z:
+    "silu_before": rmsnorm_groups(y * silu(z)) * gain; "silu": rmsnorm_groups(y) * gain * silu(z); "sigmoid": ... * sigmoid(z);
+    "plain": ... * z. `out_scale` multiplies the result.
     y float32 [n, width]; z [n, width] (may be a block of columns of wider rows); gain float32 [width]."""
+    if gate not in GATE_MODES:
+        raise KernelError(f"gated_group_rmsnorm: gate {gate!r} is not known (one of {sorted(GATE_MODES)})")
     _req(y, "y", torch.float32, 2)
     if not z.is_cuda or z.dim() != 2 or z.stride(1) != 1 or z.shape != y.shape:
         raise KernelError("gated_group_rmsnorm: z must match y, with contiguous rows")
@@ -1163,8 +1203,107 @@ def gated_group_rmsnorm(y, z, gain, eps: float, out, groups: int) -> None:
     n, width = y.shape
     if gain.numel() != width or out.shape != y.shape or groups <= 0 or width % groups:
         raise KernelError("gated_group_rmsnorm: shapes do not agree")
-    _call("norm", "gated_group_rmsnorm", library().qi_gated_group_rmsnorm, _ptr(y), _ptr(z), _code(z), C.c_longlong(z.stride(0)),
-          _ptr(gain), C.c_float(eps), _ptr(out), _code(out), n, width, groups, _stream())
+    _call("norm", "gated_group_rmsnorm", library().qi_group_rmsnorm_gate, _ptr(y), _ptr(z), _code(z), C.c_longlong(z.stride(0)),
+          _ptr(gain), C.c_float(eps), _ptr(out), _code(out), n, width, groups, GATE_MODES[gate], C.c_float(out_scale), _stream())
+
+
+# --------------------------------------------------------------------------
+# recurrent mixers with a state of fixed size
+
+
+def _cols(t, name: str, dtype=None) -> None:
+    """A block of columns of wider rows: [n, c] with unit stride inside a row."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.stride(0) < t.shape[1]:
+        raise KernelError(f"{name} must be a CUDA tensor [n, columns] whose rows are contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def mingru_scan(proj, bz, bx, state, out, q_start, start_pos, slot_ids, width: int, slices: int = 1) -> None:
+    """S_t = (1 - z) S_(t-1) + z c, out_t = S_t silu(g) per channel over each entry's tokens, with z = sigmoid(pz + bz),
+    u = px + bx, c = u + 1/2 where u >= 0 and sigmoid(u) below. proj [n, 3 width] holds pz | px | pg (it may be a block of
+    columns of wider rows); state float32 [slots, width] (read at an entry's first token unless it starts its sequence,
+    written after its last); out [n, width]. `slices`: parts an entry is cut into that run side by side (1 .. 32)."""
+    _cols(proj, "proj")
+    _req(bz, "bz", torch.float32, 1)
+    _req(bx, "bx", torch.float32, 1)
+    _req_state(state, "state", torch.float32)
+    _req(out, "out", ndim=2)
+    n = proj.shape[0]
+    if proj.shape[1] != 3 * width or bz.numel() != width or bx.numel() != width or tuple(out.shape) != (n, width) or tuple(
+            state.shape[1:]) != (width,):
+        raise KernelError("mingru_scan: shapes do not agree")
+    for t, name in ((q_start, "q_start"), (start_pos, "start_pos"), (slot_ids, "slot_ids")):
+        _req(t, name, torch.int32, 1)
+    _call("scan", "mingru_scan", library().qi_mingru_scan, _ptr(proj), C.c_longlong(proj.stride(0)), _code(proj), _ptr(bz), _ptr(bx),
+          _ptr(state), C.c_longlong(state.stride(0)), _ptr(out), _code(out), _ptr(q_start), _ptr(start_pos), _ptr(slot_ids),
+          start_pos.numel(), width, int(slices), _stream())
+
+
+def token_shift(h, mu, state, out, token_req, q_start, start_pos, slot_ids) -> None:
+    """out[s, t] = h[t] + (h[t - 1] - h[t]) * mu[s]: every token's input mixed with its predecessor's, once per row of
+    mu. h [n, C]; mu float32 [mixes, C]; state float32 [slots, C]: the last input of a request's step before (zeros at a
+    sequence's start), replaced by this step's last; out [mixes, n, C] in h's type."""
+    _req(h, "h", ndim=2)
+    _req(mu, "mu", torch.float32, 2)
+    _req_state(state, "state", torch.float32)
+    _req(out, "out", h.dtype, 3)
+    n, ch = h.shape
+    if mu.shape[1] != ch or tuple(out.shape) != (mu.shape[0], n, ch) or tuple(state.shape[1:]) != (ch,):
+        raise KernelError("token_shift: shapes do not agree")
+    for t, name in ((token_req, "token_req"), (q_start, "q_start"), (start_pos, "start_pos"), (slot_ids, "slot_ids")):
+        _req(t, name, torch.int32, 1)
+    _call("other", "token_shift", library().qi_token_shift, _ptr(h), _code(h), _ptr(mu), _ptr(state), C.c_longlong(state.stride(0)),
+          _ptr(out), _ptr(token_req), _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), n, ch, mu.shape[0], _stream())
+
+
+def matrix_state_scan(mode: str, r, k, v, state, o, q_start, start_pos, slot_ids, heads: int, dk: int, dv: int, *, log_decay=None,
+                      decay_bias=None, bonus=None, head_decay=None) -> None:
+    """A recurrence over a matrix state S [dk, dv] a head that decays and receives k_t v_t^T with every token.
+    mode "channel_decay": o_t = S_(t-1)^T r_t + (sum_i r_i bonus_i k_i) v_t, then S_t = diag(w_t) S_(t-1) + k_t v_t^T with
+    w_t = exp(-exp(log_decay_t + decay_bias)) per head and key channel. mode "head_decay": r, k, v pass silu first,
+    S_t = head_decay S_(t-1) + k_t v_t^T, o_t = S_t^T r_t. r, k, log_decay [n, heads dk], v [n, heads dv] (blocks of
+    columns of wider rows are fine); decay_bias, bonus float32 [heads dk]; head_decay float32 [heads]; state float32
+    [slots, heads, dv, dk]; o float32 [n, heads dv]."""
+    if mode not in ("channel_decay", "head_decay"):
+        raise KernelError(f"matrix_state_scan: unknown mode {mode!r}")
+    for t, name in ((r, "r"), (k, "k"), (v, "v")):
+        _cols(t, name, r.dtype)
+    n = r.shape[0]
+    if r.shape[1] != heads * dk or k.shape != r.shape or tuple(v.shape) != (n, heads * dv):
+        raise KernelError("matrix_state_scan: r, k, v do not fit the heads")
+    channel = mode == "channel_decay"
+    if channel:
+        _cols(log_decay, "log_decay", r.dtype)
+        _req(decay_bias, "decay_bias", torch.float32)
+        _req(bonus, "bonus", torch.float32)
+        if log_decay.shape != r.shape or decay_bias.numel() != heads * dk or bonus.numel() != heads * dk:
+            raise KernelError("matrix_state_scan: the decay's operands do not fit the heads")
+    else:
+        _req(head_decay, "head_decay", torch.float32, 1)
+        if head_decay.numel() != heads:
+            raise KernelError("matrix_state_scan: one decay a head")
+    _req_state(state, "state", torch.float32)
+    _req(o, "o", torch.float32, 2)
+    if tuple(state.shape[1:]) != (heads, dv, dk) or tuple(o.shape) != (n, heads * dv):
+        raise KernelError(f"matrix_state_scan: state {tuple(state.shape)} / o {tuple(o.shape)} do not fit")
+    for t, name in ((q_start, "q_start"), (start_pos, "start_pos"), (slot_ids, "slot_ids")):
+        _req(t, name, torch.int32, 1)
+    _call("scan", "matrix_state_scan", library().qi_matrix_state_scan, 0 if channel else 1, _ptr(r), C.c_longlong(r.stride(0)), _ptr(k),
+          C.c_longlong(k.stride(0)), _ptr(v), C.c_longlong(v.stride(0)), _ptr(log_decay), C.c_longlong(log_decay.stride(0) if channel else 0),
+          _code(r), _ptr(decay_bias), _ptr(bonus), _ptr(head_decay), _ptr(state), C.c_longlong(state.stride(0)), _ptr(o),
+          _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), start_pos.numel(), heads, dk, dv, _stream())
+
+
+def scaled_sum(a, b, sa: float, sb: float, out) -> None:
+    """out = sa * a + sb * b in 32-bit; a, b of one type and shape, out float32."""
+    _req(a, "a")
+    _req(b, "b", a.dtype)
+    _req(out, "out", torch.float32)
+    if a.shape != b.shape or out.shape != a.shape:
+        raise KernelError("scaled_sum: shapes differ")
+    _call("other", "scaled_sum", library().qi_scaled_sum, _ptr(a), _ptr(b), _code(a), C.c_float(sa), C.c_float(sb), _ptr(out),
+          C.c_longlong(a.numel()), _stream())
 
 
 def glu_clamped(gate_up, out, limit: float, alpha: float, interleaved: bool = False) -> None:
@@ -1283,13 +1422,16 @@ def gated_attention_mma_supported(nq: int, nkv: int, d: int, dv: int) -> bool:
 
 
 def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv, scale: float, window: int, chunk: int, gate,
-                    status, impl: str | None = None) -> None:
+                    status, impl: str | None = None, softcap: float = 0.0, out_scale: float = 1.0) -> None:
     """Attention with separate key and value sizes, an optional chunk bound and an optional output gate, by the
     kernel that fits: "mma" (bfloat16, head sizes that are multiples of 8 up to 128: flash form on the tensor
     cores, tiles found on the device from the step's arrays) or "generic" (32-bit arithmetic, any sizes). A step
     with prompt portions whose keys and values are both of size 128 goes to "tcgen05": the portions' query tiles
-    to the tcgen05 flash kernel (chunk bound and gate included), the single tokens in front of them to "mma"."""
-    if impl is None and q.dtype == torch.bfloat16 and d == dv and not batch.all_decode and batch.tile_req.numel() and (
+    to the tcgen05 flash kernel (chunk bound and gate included), the single tokens in front of them to "mma".
+    `softcap` c > 0 (a score s becomes c tanh(s / c)) and `out_scale` (a factor on the result) are known to "mma" and
+    "generic"."""
+    plain = not softcap and out_scale == 1.0
+    if impl is None and plain and q.dtype == torch.bfloat16 and d == dv and not batch.all_decode and batch.tile_req.numel() and (
             gate is None or (gate.stride(0) % 8 == 0 and gate.data_ptr() % 16 == 0)) and attention_prefill_tcgen05_supported(
             nq, nkv, d, k_pages.shape[2], block_table.shape[1]):
         impl = "tcgen05"
@@ -1298,6 +1440,8 @@ def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv
         if lead:
             gated_attention(q[:lead], out[:lead], k_pages, v_pages, block_table[:lead], _LeadRows(batch, lead), nq, nkv, d, dv,
                             scale, window, chunk, gate[:lead] if gate is not None else None, status, impl="mma")
+        if not plain:
+            raise KernelError("gated_attention: the tcgen05 kernel knows neither a soft cap nor an output factor")
         return attention_prefill(q, out, k_pages, v_pages, block_table, batch.q_start, batch.start_pos, batch.tile_req,
                                  batch.tile_q0, nq, nkv, d, scale, window, status, impl="tcgen05", max_kv_len=batch.max_kv_len,
                                  key_ranges=1 if chunk else None, chunk=chunk, gate=gate)
@@ -1306,7 +1450,7 @@ def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv
             gate is None or gate.stride(0) % 2 == 0) else "generic"
     if impl == "generic":
         return attention_generic(q, out, k_pages, v_pages, block_table, batch.positions, batch.token_req, nq, nkv, d, scale,
-                                 window, status, chunk=chunk, gate=gate)
+                                 window, status, chunk=chunk, gate=gate, softcap=softcap, out_scale=out_scale)
     _req(q, "q", torch.bfloat16, 2)
     _req(out, "out", torch.bfloat16, 2)
     _req(k_pages, "k_pages", torch.bfloat16, 4)
@@ -1324,5 +1468,6 @@ def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv
         ldg = gate.stride(0)
     _call("attention", "gated_attention_mma", library().qi_gated_attention_mma, _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages),
           _ptr(block_table), block_table.shape[1], k_pages.shape[2], k_pages.shape[0], _ptr(batch.q_start), _ptr(batch.start_pos),
-          batch.n_requests, n, nq, nkv, d, dv, C.c_float(scale), int(window or 0), int(chunk or 0), _ptr(gate), C.c_longlong(ldg),
+          batch.n_requests, n, nq, nkv, d, dv, C.c_float(scale), C.c_float(softcap or 0.0), C.c_float(out_scale), int(window or 0),
+          int(chunk or 0), _ptr(gate), C.c_longlong(ldg),
           _ptr(status), _stream())

@@ -50,6 +50,65 @@ class PreNormBlock(Part):
         return resid, self.ffn.forward(x)
 
 
+class ConvPreNormBlock(Part):
+    """The pre-norm block whose mixer reads the normalised stream plus a causal convolution of it over time:
+
+        h = norm1(x) ; x = x + mixer(h + conv(h)) ; x = x + ffn(norm2(x))
+
+    The norm's output stays 32-bit on its way into the convolution, whose last taps - 1 inputs are the block's state of
+    fixed size; the convolution's output comes in the activation type. Without `conv` in the spec this is the plain
+    pre-norm block; the feed-forward (with its norm) may be absent. A mixer that keeps state of fixed size beside its
+    pages says so with `state_need`, which the block passes on."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.mixer_norm = build_part("norm", spec.mixer_norm, runtime)
+        self.mixer = build_part("mixer", spec.mixer, runtime)
+        self.conv = build_part("conv", spec.conv, runtime) if spec.conv is not None else None
+        self.ffn = build_part("ffn", spec.ffn, runtime) if spec.ffn is not None else None
+        self.ffn_norm = build_part("norm", spec.ffn_norm, runtime) if spec.ffn is not None else None
+        if self.conv is not None and len(spec.conv.names) != 1:
+            raise ConfigError("prenorm_conv: one input filter (the mixer's)")
+        self._parts = tuple(p for p in (self.mixer_norm, self.mixer, self.conv, self.ffn_norm, self.ffn) if p is not None)
+
+    @classmethod
+    def needs_of_spec(cls, spec):
+        needs = {}
+        subs = [("norm", spec.mixer_norm), ("mixer", spec.mixer)]
+        if spec.conv is not None:
+            subs.append(("conv", spec.conv))
+        if spec.ffn is not None:
+            subs += [("norm", spec.ffn_norm), ("ffn", spec.ffn)]
+        for cat, sub in subs:
+            needs.update(part_class(cat, sub).needs_of_spec(sub))
+        return needs
+
+    def load(self, tensors):
+        for p in self._parts:
+            p.load(tensors)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def state_need(self):
+        return self.conv.state_need() if self.conv is not None else None
+
+    def mixer_state_need(self):
+        return getattr(self.mixer, "state_need", lambda: None)()
+
+    def forward(self, resid, delta, batch, cache):
+        if self.conv is not None:
+            wide = getattr(self.mixer_norm, "wide_output", False)      # a norm that can hand its result on in 32-bit does
+            h = self.mixer_norm(resid, delta, out_dtype=torch.float32) if wide else self.mixer_norm(resid, delta)
+            (x,), _ = self.conv.forward(h, batch, cache.block_state)
+        else:
+            x = self.mixer_norm(resid, delta)
+        y = self.mixer.forward(x, batch, cache)
+        if self.ffn is None:
+            return resid, y
+        return resid, self.ffn.forward(self.ffn_norm(resid, y))
+
+
 class ParallelGatedBlock(Part):
     """One norm, two sublayers side by side, gated:
 
@@ -121,7 +180,7 @@ class ParallelGatedBlock(Part):
         if self.conv is not None:
             h = torch.empty((n, width), dtype=torch.float32, device=resid.device)
             kernels.add_rmsnorm(resid, delta, self.norm.gain, self.norm.spec.eps, h)
-            ins, hb = self.conv.forward(h, batch, cache.state, want_copy=rt.dtype != torch.float32)
+            ins, hb = self.conv.forward(h, batch, cache.block_state, want_copy=rt.dtype != torch.float32)
             if hb is None:
                 hb = h
         else:
@@ -190,4 +249,5 @@ class SandwichBlock(Part):
 
 register_part("block", "prenorm", PreNormBlock)
 register_part("block", "sandwich", SandwichBlock)
+register_part("block", "prenorm_conv", ConvPreNormBlock)
 register_part("block", "parallel_gated", ParallelGatedBlock)

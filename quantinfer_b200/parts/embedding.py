@@ -35,7 +35,7 @@ class Embedding(Part):
 
     def forward(self, token_ids):
         out = torch.empty((token_ids.numel(), self.spec.hidden_size), dtype=torch.float32, device=token_ids.device)
-        kernels.embedding(self.table.weight, token_ids, out, self.runtime.status)
+        kernels.embedding(self.table.weight, token_ids, out, self.runtime.status, scale=getattr(self.spec, "scale", 1.0))
         return out
 
     __call__ = forward

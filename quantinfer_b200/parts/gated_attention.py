@@ -1,10 +1,15 @@
 """Causal grouped-query attention with biased projections, an output gate and chunks.
 
     [q | k | v | g] = x . W^T                 (the four projections stacked at load: one product)
+    q | k | v       = conv(q | k | v)         (optional: a causal convolution over time per channel, `conv_taps` taps)
     q, k            = rotate(q + b_q, p), rotate(k + b_k, p)      over the first `rotary_dim` coordinates of a head
     cache[p]        = (k, v + b_v)            values may have another size than keys
-    a               = softmax(q k^T * scale over the visible keys) v
-    y               = (a * sigmoid(g)) . Wo^T (+ b_o)
+    a               = softmax(cap(q k^T * scale) over the visible keys) v          cap(s) = c tanh(s / c), optional
+    y               = (a * sigmoid(g) * out_scale) . Wo^T (+ b_o)
+
+Biases, the gate, the convolution, the cap and the factor are each optional (fields of the spec). The convolution's
+last taps - 1 projected rows are the mixer's state of fixed size BESIDE its pages (`state_need`, handed back as
+`cache.mixer_state`).
 
 Visible keys of the query at position i: j <= i, within the last `window` positions if the spec has a window, and
 within i's own chunk (floor(i / chunk) = floor(j / chunk), chunks counted from the sequence's first position, not
@@ -22,7 +27,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from ..cache.needs import PagedKVNeed
+from ..cache.needs import PagedKVNeed, StateNeed
 from ..errors import ConfigError
 from ..weights.loader import TensorNeed
 from .base import Part, register_part
@@ -42,7 +47,10 @@ class GatedAttention(Part):
         self.qkv_cols = (self.H + self.G) * self.d + self.G * self.dv
         self.proj = Linear(runtime, self.qkv_cols + (self.H * self.dv if s.out_gate else 0), s.hidden_size, s.prefix + "q+k+v+g")
         self.o = Linear(runtime, s.hidden_size, self.H * self.dv, s.prefix + "o")
-        self.bias = self.out_bias = self.inv_freq = None
+        self.bias = self.out_bias = self.inv_freq = self.conv_w = None
+        self.taps = getattr(s, "conv_taps", None)
+        if self.taps is not None and not 1 <= self.taps <= 16:
+            raise ConfigError(f"gated_attention: a convolution of {self.taps} taps (1..16)")
         pos = s.position
         self.rot = pos.rotary_dim if pos is not None else 0
         self.interleaved = pos is not None and pos.pairing == "interleaved"
@@ -59,6 +67,9 @@ class GatedAttention(Part):
         if s.out_gate:
             needs[p + "g"] = TensorNeed((H * dv, w))
         needs[p + "o"] = TensorNeed((w, H * dv))
+        if getattr(s, "conv_taps", None) is not None:
+            needs.update({p + "q.conv": TensorNeed((H * d, s.conv_taps)), p + "k.conv": TensorNeed((G * d, s.conv_taps)),
+                          p + "v.conv": TensorNeed((G * dv, s.conv_taps))})
         if s.bias:
             needs.update({p + "q.b": TensorNeed((H * d,), "matrix", "zeros"), p + "k.b": TensorNeed((G * d,), "matrix", "zeros"),
                           p + "v.b": TensorNeed((G * dv,), "matrix", "zeros"), p + "o.b": TensorNeed((w,), "matrix", "zeros")})
@@ -71,6 +82,9 @@ class GatedAttention(Part):
             ws = [t.to(torch.float32) for t in ws]
         self.proj.load(torch.cat(ws, dim=0))
         self.o.load(tensors[p + "o"])
+        if self.taps is not None:
+            w = torch.cat([tensors[p + n + ".conv"].to(torch.float32) for n in ("q", "k", "v")], dim=0)
+            self.conv_w = self._gain(w.t().unsqueeze(0))          # [1, taps, q | k | v channels]
         if s.bias:
             self.bias = self._gain(torch.cat([tensors[p + n + ".b"].to(torch.float32) for n in ("q", "k", "v")]))
             self.out_bias = self._gain(tensors[p + "o.b"])
@@ -78,19 +92,33 @@ class GatedAttention(Part):
     def cache_need(self):
         return PagedKVNeed(self.G, self.d, self.spec.window, self.dv if self.dv != self.d else None, self.spec.chunk)
 
+    def state_need(self):
+        """The convolution's state: the last taps - 1 rows of q | k | v as projected (32-bit), beside the pages."""
+        if self.taps is None or self.taps < 2:
+            return None
+        return StateNeed((self.taps - 1, self.qkv_cols), torch.float32)
+
     def forward(self, x, batch, cache):
         rt, s = self.runtime, self.spec
         n = x.shape[0]
         table = batch.block_tables[cache.group]
         proj = self.proj(x)
+        if self.taps is not None:
+            conved = torch.empty((n, self.qkv_cols), dtype=x.dtype, device=x.device)
+            kernels.short_conv(proj[:, :self.qkv_cols], self.conv_w, cache.mixer_state, [conved], None, batch.token_req, batch.q_start,
+                               batch.start_pos, batch.slot_ids, residual=False)
+            gate_src, proj = proj, conved
+        else:
+            gate_src = proj
         q = torch.empty((n, self.H * self.d), dtype=x.dtype, device=x.device)
         kernels.bias_rope_kv(proj, self.bias, q, self.inv_freq, self.rot, self.interleaved, batch.positions, batch.token_req,
                              table, cache.page_size, cache.k_pages if cache.writes else None,
                              cache.v_pages if cache.writes else None, self.H, self.G, self.d, self.dv, rt.status)
         out = torch.empty((n, self.H * self.dv), dtype=x.dtype, device=x.device)
-        gate = proj[:, self.qkv_cols:] if s.out_gate else None
+        gate = gate_src[:, self.qkv_cols:] if s.out_gate else None
         kernels.gated_attention(q, out, cache.k_pages, cache.v_pages, table, batch, self.H, self.G, self.d, self.dv, s.scale,
-                                s.window or 0, s.chunk or 0, gate, rt.status)
+                                s.window or 0, s.chunk or 0, gate, rt.status, softcap=getattr(s, "softcap", None) or 0.0,
+                                out_scale=getattr(s, "out_scale", 1.0))
         return self.o(out, keep_partials=True)
 
 

@@ -137,6 +137,36 @@ class DynamicTanh(Part):
     __call__ = forward
 
 
+class LayerNorm(Part):
+    """Layer norm with gain and bias, the residual add fused in: x = resid + delta; out = (x - mean) / sqrt(var + eps) * w
+    + b, var the mean squared deviation (two 32-bit sums over the row). w is the tensor named by the spec's `prefix`
+    itself, b `prefix.b`. `out_dtype` float32 keeps the result in 32-bit for a consumer that wants it so (an input
+    convolution whose state is 32-bit)."""
+
+    wide_output = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.gain = self.bias = None
+
+    @classmethod
+    def needs_of_spec(cls, spec):
+        return {spec.prefix: TensorNeed((spec.size,), "gain", "gain"), spec.prefix + ".b": TensorNeed((spec.size,), "gain", "zeros")}
+
+    def load(self, tensors):
+        self.gain, self.bias = self._gain(tensors[self.spec.prefix]), self._gain(tensors[self.spec.prefix + ".b"])
+
+    def forward(self, resid, delta, rows=None, write_resid=True, out_dtype=None):
+        delta = settle(resid, delta)
+        n = resid.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.spec.size), dtype=out_dtype or self.runtime.dtype, device=resid.device)
+        kernels.add_layernorm(resid, delta, self.gain, self.bias, self.spec.eps, out, rows=rows, write_resid=write_resid)
+        return out
+
+    __call__ = forward
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)
 register_part("norm", "dyt", DynamicTanh)
 register_part("norm", "rmsnorm_scalar", ScalarRMSNorm)

@@ -42,9 +42,17 @@ from .safetensors_io import SafeTensorsFolder
 
 @dataclass(frozen=True)
 class TensorNeed:
-    shape: tuple
+    shape: tuple             # a dimension may be None: any size (the part reads it from the tensor it is given)
     kind: str = "matrix"     # "matrix" | "table" (embedding) | "gain" | "int"
     init: str = "normal"     # how random weights fill it: "normal" | "gain" | "zeros"
+    free: int = 16           # the size a None dimension gets when weights are drawn at random
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(w is None or w == h for w, h in zip(self.shape, shape))
+
+    def drawn_shape(self) -> tuple:
+        return tuple(self.free if s is None else s for s in self.shape)
 
 
 def check_and_load(source, needs: dict, *, strict: bool = False, check_finite: bool = False, warn=None) -> dict:
@@ -60,8 +68,8 @@ def check_and_load(source, needs: dict, *, strict: bool = False, check_finite: b
     for name in sorted(want & have):
         need = needs[name]
         shape = tuple(source.shape(name))
-        if shape != tuple(need.shape):
-            wrong_shape.append(f"{name}: has {list(shape)}, expected {list(need.shape)}")
+        if not need.fits(shape):
+            wrong_shape.append(f"{name}: has {list(shape)}, expected {['any' if d is None else d for d in need.shape]}")
         dt = source.dtype(name)
         is_float = dt in (torch.float32, torch.float16, torch.bfloat16)
         if (need.kind == "int") == is_float:

@@ -27,6 +27,8 @@ GAIN_SPREAD = 0.1
 def random_tensor(need: TensorNeed, seed: int, index: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
     g = torch.Generator(device=device)
     g.manual_seed((int(seed) * 1000003 + index) % (1 << 63))
+    if any(d is None for d in need.shape):
+        need = TensorNeed(need.drawn_shape(), need.kind, need.init)
     if need.kind == "int":
         return torch.zeros(need.shape, dtype=torch.int32, device=device)
     if need.init == "gain":
