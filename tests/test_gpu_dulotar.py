@@ -1,0 +1,645 @@
+"""The Dulotar design on the GPU against the plain implementation (tests/plain/plain_dulotar.py): every mechanism
+alone, then whole models replayed whole, token by token, in portions down to two tokens and mixed with other
+requests on a pool so small that pages and slots are used again; generation through the scheduler.
+
+Where random weights would hide a fault the inputs are made so that it shows: one key whose score stands out for
+every query of its chunk and for none of the next, scores far beyond the cap, a recurrent state carried over hundreds
+of steps, a slot whose earlier owner left its state behind."""
+
+import json
+import math
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from dulotar_tools import CONFIGS, PAGE_SIZES, clean, draw_weights, left, make, mingru, model, parallel, plain_rows, right, wkv, write_folder
+from helpers import random_tokens
+from plain import plain_dulotar as plain
+from trace_tools import ROOT, collect, mixed_trace, portions_trace, round64, run_trace_engine, tail_trace, whole_trace
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+# |engine - plain float64| on logits of a few units. float32: the order of sums and the device's exp, tanh, sin, cos.
+# Measured: median 2e-6 to 7e-6, worst 5.4e-5 (rows whose norms divide by little carry eight to twenty times the median);
+# the bound is three times the worst. bfloat16: median 0.04 to 0.08 with the same few rows at 0.4 to 0.9: most rows within
+# three times the median, a few of a hundred beyond it, none beyond 1.5.
+TOL_F32 = 1.5e-4
+TOL_BF16 = {"U": 0.2, "V": 0.3, "W": 0.2}
+BF16_ROWS_BEYOND, BF16_WORST = 0.04, 1.5
+LENGTHS = {"U": [70, 45, 100, 33, 2, 64, 17, 1], "V": [130, 64, 97, 33, 260, 5], "W": [50, 33, 80, 17, 64, 9]}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("dulotar")
+    return {name: make(root / name, name) for name in CONFIGS}
+
+
+def _requests(name):
+    v = CONFIGS[name]["vocab"]
+    return {f"{name}{i}": random_tokens(n, v, seed=31 * i + n) for i, n in enumerate(LENGTHS[name])}
+
+
+_expected = {}
+
+
+def _expect(models, name):
+    if name not in _expected:
+        _, cfg, w = models[name]
+        _expected[name] = plain_rows(cfg, w, _requests(name))
+    return _expected[name]
+
+
+def _compare(got, expect, name, dtype, what=""):
+    assert set(got) == set(expect)
+    errs = {k: float(np.abs(got[k].astype(np.float64) - expect[k].astype(np.float64)).max()) for k in expect}
+    worst = max(errs, key=errs.get)
+    print(f"measured {name} {dtype} {what}: median {np.median(list(errs.values())):.3g}, worst {errs[worst]:.3g} at {worst}")
+    if dtype == "float32":
+        assert errs[worst] <= TOL_F32, f"worst difference {errs[worst]} at (request, position) {worst}"
+        return
+    beyond = sorted(k for k in errs if errs[k] > TOL_BF16[name])
+    assert len(beyond) <= max(1, BF16_ROWS_BEYOND * len(errs)) and errs[worst] <= BF16_WORST, (len(beyond), len(errs), errs[worst], worst)
+
+
+def _d(t):
+    return t.to(DEV)
+
+
+def _i(v):
+    return torch.tensor(v, dtype=torch.int32, device=DEV)
+
+
+def _entries(lens, starts):
+    """The step arrays of entries with these lengths and first positions, each in its own slot."""
+    q0 = [0] + np.cumsum(lens).tolist()
+    token_req = [e for e, n in enumerate(lens) for _ in range(n)]
+    return _i(q0), _i(starts), _i(list(range(len(lens)))), _i(token_req)
+
+
+# ---------------------------------------------------------------- small kernels against their formulas
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("h", [44, 64, 1000])
+def test_layer_norm_with_the_residual_update_fused_in(dtype, h):
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(h)
+    n = 37
+    resid = torch.randn(n, h) * 3.0 + 1.5            # a mean far from zero: the variance is of the deviations
+    delta = torch.randn(n, h).to(dtype)
+    gain, bias = torch.randn(h), torch.randn(h) * 0.3
+    x = resid.double() + delta.double()
+    ref = plain.layer_norm(x, gain, bias, 1e-5)
+    r = _d(resid.clone())
+    for out_dtype in (dtype, torch.float32):
+        r = _d(resid.clone())
+        out = torch.empty(n, h, dtype=out_dtype, device=DEV)
+        k.add_layernorm(r, _d(delta), _d(gain), _d(bias), 1e-5, out)
+        assert float((r.cpu().double() - x).abs().max()) < 2e-6
+        assert float((out.cpu().double() - ref).abs().max()) < (5e-6 if out_dtype == torch.float32 else 0.04)
+    # picked rows: the stream is read, not written; partial sums of a product cut along K
+    rows = torch.tensor([5, 0, 36, 5], dtype=torch.int32)
+    parts = torch.randn(3, n, h)
+    r2 = _d(resid.clone())
+    out2 = torch.empty(4, h, dtype=torch.float32, device=DEV)
+    k.add_layernorm(r2, _d(parts), _d(gain), None, 1e-5, out2, rows=_d(rows))
+    assert torch.equal(r2.cpu(), resid)
+    ref2 = plain.layer_norm(resid.double() + parts.double().sum(0), gain, torch.zeros(h), 1e-5)[rows.long()]
+    assert float((out2.cpu().double() - ref2).abs().max()) < 5e-6
+
+
+def test_embedding_rows_are_scaled_in_32_bit():
+    from quantinfer_b200 import kernels as k
+
+    table = torch.randn(50, 24).to(torch.bfloat16)
+    ids = torch.tensor([3, 49, 0, 3], dtype=torch.int32)
+    out = torch.empty(4, 24, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    k.embedding(_d(table), _d(ids), out, status, scale=17.25)
+    assert torch.equal(out.cpu(), table.float()[ids.long()] * 17.25) and int(status.item()) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_squared_relu_and_tanh(dtype):
+    from quantinfer_b200 import kernels as k
+
+    x = (torch.randn(33, 40) * 2.0).to(dtype)
+    for name, f in (("relu2", lambda v: torch.relu(v) ** 2), ("tanh", torch.tanh)):
+        out = torch.empty_like(x, device=DEV)
+        k.activation(_d(x), out, name)
+        ref = f(x.double())
+        assert float(((out.cpu().double() - ref).abs() / (1.0 + ref.abs())).max()) < (1e-6 if dtype == torch.float32 else 0.01)
+
+
+@pytest.mark.parametrize("gate, groups", [("silu", 3), ("sigmoid", 1), ("plain", 2), ("silu_before", 3)])
+def test_group_norm_with_its_gates(gate, groups):
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(1)
+    n, w = 19, 42
+    y, z, gain = torch.randn(n, w) * 4.0, torch.randn(n, w + 6).to(torch.bfloat16), torch.randn(w)
+    zz = z[:, 3:3 + w].double()
+    g = {"silu": plain.silu(zz), "sigmoid": torch.sigmoid(zz), "plain": zz, "silu_before": plain.silu(zz)}[gate]
+    yy = y.double() * g if gate == "silu_before" else y.double()
+    ref = plain.unit_rms(yy.view(n, groups, -1), 1e-5).reshape(n, w) * gain.double()
+    if gate != "silu_before":
+        ref = ref * g
+    out = torch.empty(n, w, dtype=torch.float32, device=DEV)
+    k.gated_group_rmsnorm(_d(y), _d(z)[:, 3:3 + w], _d(gain), 1e-5, out, groups, gate=gate, out_scale=0.75)
+    assert float((out.cpu().double() - 0.75 * ref).abs().max()) < 1e-5
+
+
+def test_the_sum_of_two_branches():
+    from quantinfer_b200 import kernels as k
+
+    a, b = torch.randn(21, 30).to(torch.bfloat16), torch.randn(21, 30).to(torch.bfloat16)
+    out = torch.empty(21, 30, dtype=torch.float32, device=DEV)
+    k.scaled_sum(_d(a), _d(b), 1.2, 0.5, out)
+    assert float((out.cpu().double() - (1.2 * a.double() + 0.5 * b.double())).abs().max()) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("slices", [1, 4, 32])
+def test_the_gated_recurrence_kernel(dtype, slices):
+    """Entries of 1, 2, 70 and 300 tokens side by side; two continue sequences whose slots hold a state, one starts a
+    sequence in a slot that holds somebody else's; columns of wider rows; slices that are mostly empty."""
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(2)
+    w, lens, starts = 37, [1, 70, 2, 300], [5, 0, 9, 40]
+    n = sum(lens)
+    wide = (torch.randn(n, 3 * w + 5) * 1.5).to(dtype)
+    bz, bx = torch.randn(w) * 0.5 - 1.0, torch.randn(w) * 0.3
+    state = torch.randn(4, w + 3)
+    q0, sp, slots, _ = _entries(lens, starts)
+    out = torch.empty(n, w, dtype=dtype, device=DEV)
+    st = _d(state.clone())
+    k.mingru_scan(_d(wide)[:, 2:2 + 3 * w], _d(bz), _d(bx), st[:, :w], out, q0, sp, slots, w, slices)
+    a = 0
+    for e, ln in enumerate(lens):
+        p = wide[a:a + ln, 2:2 + 3 * w].double()
+        z = torch.sigmoid(p[:, :w] + bz.double())
+        u = p[:, w:2 * w] + bx.double()
+        c = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+        S = state[e, :w].double() if starts[e] > 0 else torch.zeros(w, dtype=torch.float64)
+        for t in range(ln):
+            S = (1 - z[t]) * S + z[t] * c[t]
+            ref = S * plain.silu(p[t, 2 * w:])
+            assert float((out[a + t].cpu().double() - ref).abs().max()) < (2e-5 if dtype == torch.float32 else 0.03), (e, t)
+        assert float((st[e, :w].cpu().double() - S).abs().max()) < 2e-5
+        assert torch.equal(st[e, w:].cpu(), state[e, w:])
+        a += ln
+
+
+def test_token_shift_and_its_state():
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(3)
+    C, lens, starts = 29, [3, 1, 1, 40], [0, 7, 0, 12]
+    n = sum(lens)
+    h, mu, state = torch.randn(n, C), torch.rand(5, C), torch.randn(4, C + 2)
+    q0, sp, slots, token_req = _entries(lens, starts)
+    out = torch.empty(5, n, C, dtype=torch.float32, device=DEV)
+    st = _d(state.clone())
+    k.token_shift(_d(h), _d(mu), st[:, :C], out, token_req, q0, sp, slots)
+    a = 0
+    for e, ln in enumerate(lens):
+        first = state[e, :C] if starts[e] > 0 else torch.zeros(C)
+        prev = torch.cat([first[None], h[a:a + ln - 1]])
+        for s in range(5):
+            ref = h[a:a + ln] + (prev - h[a:a + ln]) * mu[s]
+            assert float((out[s, a:a + ln].cpu() - ref).abs().max()) < 1e-6
+        assert torch.equal(st[e, :C].cpu(), h[a + ln - 1]) and torch.equal(st[e, C:].cpu(), state[e, C:])
+        a += ln
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads, dk, dv", [(3, 6, 6), (2, 32, 32), (1, 40, 70), (2, 100, 8), (1, 130, 20), (2, 16, 130)])
+@pytest.mark.parametrize("mode", ["channel_decay", "head_decay"])
+def test_the_matrix_state_recurrences(dtype, heads, dk, dv, mode):
+    """Both recurrences over a matrix state a head: keys of 6 to 130 numbers (padded to the next size the kernel has),
+    more value columns than a block takes, entries of 1, 2, 19 and 45 tokens, slots with and without an earlier state."""
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(dk + dv)
+    lens, starts = [1, 19, 2, 45], [3, 0, 0, 11]
+    n = sum(lens)
+    r = (torch.randn(n, heads * dk + 3) * 0.7).to(dtype)
+    kk = (torch.randn(n, heads * dk) * 0.7).to(dtype)
+    v = (torch.randn(n, heads * dv + 1) * 0.7).to(dtype)
+    lw = (torch.randn(n, heads * dk) * 0.5).to(dtype)
+    w0, u, lam = -0.5 - 3.0 * torch.rand(heads * dk), torch.randn(heads * dk) * 0.5, torch.tensor([0.9, 0.6, 0.99][:heads])
+    state = torch.randn(4, heads * dv * dk + 4) * 0.3
+    q0, sp, slots, _ = _entries(lens, starts)
+    o = torch.empty(n, heads * dv, dtype=torch.float32, device=DEV)
+    st = _d(state.clone())
+    S_dev = st[:, :heads * dv * dk].unflatten(1, (heads, dv, dk))
+    rr, vv = _d(r)[:, 3:], _d(v)[:, :heads * dv]
+    if mode == "channel_decay":
+        k.matrix_state_scan(mode, rr, _d(kk), vv, S_dev, o, q0, sp, slots, heads, dk, dv, log_decay=_d(lw), decay_bias=_d(w0), bonus=_d(u))
+    else:
+        k.matrix_state_scan(mode, rr, _d(kk), vv, S_dev, o, q0, sp, slots, heads, dk, dv, head_decay=_d(lam))
+    a = 0
+    for e, ln in enumerate(lens):
+        for hd in range(heads):
+            S = state[e, :heads * dv * dk].double().view(heads, dv, dk)[hd].T.clone() if starts[e] > 0 else torch.zeros(dk, dv, dtype=torch.float64)
+            for t in range(ln):
+                rt = r[a + t, 3 + hd * dk:3 + (hd + 1) * dk].double()
+                kt = kk[a + t, hd * dk:(hd + 1) * dk].double()
+                vt = v[a + t, hd * dv:(hd + 1) * dv].double()
+                if mode == "channel_decay":
+                    dec = torch.exp(-torch.exp(lw[a + t, hd * dk:(hd + 1) * dk].double() + w0[hd * dk:(hd + 1) * dk].double()))
+                    kv = torch.outer(kt, vt)
+                    ref = (S + u[hd * dk:(hd + 1) * dk].double()[:, None] * kv).T @ rt
+                    S = dec[:, None] * S + kv
+                else:
+                    S = float(lam[hd]) * S + torch.outer(plain.silu(kt), plain.silu(vt))
+                    ref = S.T @ plain.silu(rt)
+                got = o[a + t, hd * dv:(hd + 1) * dv].cpu().double()
+                assert float((got - ref).abs().max()) < 2e-4 * max(1.0, float(ref.abs().max())), (e, hd, t)
+            got_S = st[e, :heads * dv * dk].cpu().double().view(heads, dv, dk)[hd].T
+            assert float((got_S - S).abs().max()) < 2e-4 * max(1.0, float(S.abs().max()))
+        assert torch.equal(st[e, heads * dv * dk:].cpu(), state[e, heads * dv * dk:])
+        a += ln
+
+
+@pytest.mark.parametrize("impl, dtype", [("generic", torch.float32), ("generic", torch.bfloat16), ("mma", torch.bfloat16)])
+@pytest.mark.parametrize("H, G, d, dv, chunk, cap", [(4, 2, 16, 8, 24, 2.0), (2, 1, 64, 64, 0, 5.0), (3, 3, 40, 24, 64, 0.0), (2, 2, 8, 128, 17, 1.0)])
+def test_capped_scores_in_both_attention_kernels(impl, dtype, H, G, d, dv, chunk, cap):
+    """Scores several times the cap (so that leaving it out, or applying it after the mask, changes every row), pages in
+    shuffled order, a decode token in front of two portions, NaN in the pages no row may look at, a factor on the result."""
+    from types import SimpleNamespace
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(H * d + chunk)
+    page, lens, starts = 8, [1, 37, 20], [50, 0, 19]
+    B, n = len(lens), sum(lens)
+    ctx = [s + l for s, l in zip(starts, lens)]
+    blocks = max(-(-c // page) for c in ctx)
+    perm = torch.randperm(B * blocks + 3)
+    table = perm[:B * blocks].view(B, blocks).to(torch.int32)
+    kp = torch.zeros(B * blocks + 3, G, page, d)
+    vp = torch.zeros(B * blocks + 3, G, page, dv)
+    keys = [(torch.randn(c, G, d) * 1.5).to(torch.bfloat16).float() for c in ctx]
+    vals = [torch.randn(c, G, dv).to(torch.bfloat16).float() for c in ctx]
+    q = (torch.randn(n, H, d) * 1.5).to(torch.bfloat16).float()
+    scale, out_scale = 0.5, 1.2
+    ref = torch.zeros(n, H, dv, dtype=torch.float64)
+    a = 0
+    for e in range(B):
+        for j in range(ctx[e]):
+            kp[table[e, j // page], :, j % page] = keys[e][j]
+            vp[table[e, j // page], :, j % page] = vals[e][j]
+        for t in range(lens[e]):
+            p = starts[e] + t
+            lo = p // chunk * chunk if chunk else 0
+            for hq in range(H):
+                g = hq // (H // G)
+                s = (keys[e][lo:p + 1, g].double() @ q[a + t, hq].double()) * scale
+                if cap:
+                    s = cap * torch.tanh(s / cap)
+                ref[a + t, hq] = out_scale * (torch.softmax(s, 0) @ vals[e][lo:p + 1, g].double())
+        if chunk:
+            for b in range((starts[e] // chunk * chunk) // page):
+                kp[table[e, b]] = vp[table[e, b]] = float("nan")
+        a += lens[e]
+    q0, sp, _, token_req = _entries(lens, starts)
+    batch = SimpleNamespace(q_start=q0, start_pos=sp, n_requests=B, token_req=token_req, all_decode=False, n_lead_decode=1,
+                            positions=_i([s0 + i for s0, ln in zip(starts, lens) for i in range(ln)]), max_kv_len=max(ctx),
+                            tile_req=_i([]), tile_q0=_i([]))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((n, H * dv), float("nan"), dtype=dtype, device=DEV)
+    k.gated_attention(_d(q.view(n, H * d).to(dtype)), out, _d(kp.to(dtype)), _d(vp.to(dtype)), _d(table), batch, H, G, d, dv, scale, 0, chunk,
+                      None, status, impl=impl, softcap=cap, out_scale=out_scale)
+    assert int(status.item()) == 0
+    err = (out.cpu().double().view(n, H, dv) - ref).abs()
+    assert float(err.max()) < (1e-4 if dtype == torch.float32 else 0.04), (float(err.max()), np.unravel_index(int(err.argmax()), err.shape))
+
+
+# ---------------------------------------------------------------- one mixer alone, in an engine of one layer
+
+
+def _one_layer(tmp_path, entry, width, dtype, page_size=8, seed=77, eps=1e-6, max_tokens=512, taps=None):
+    from quantinfer_b200.engine import Engine
+
+    cfg = model(16, width, eps, 1.0, taps, [entry])
+    w = draw_weights(cfg, seed)
+    folder = write_folder(tmp_path / f"one{dtype}{seed}", cfg, w)
+    eng = Engine.from_folder(folder, dtype=dtype, page_size=page_size, max_tokens=max_tokens, max_requests=4, use_graphs=False)
+    return eng, clean(cfg), {k: v.double() for k, v in w.items()}
+
+
+def _run(eng, inputs, cuts, rid="r", part="mixer"):
+    """Feeds `inputs` [T, width] through the layer's mixer in portions `cuts` for one request."""
+    from quantinfer_b200.engine import StepEntry
+
+    eng.open(rid)
+    outs, a = [], 0
+    mixer = eng.model.blocks[0].mixer
+    for n in cuts:
+        eng.cache.prepare(rid, n)
+        batch = eng.make_batch([StepEntry(rid, [0] * n, [])])
+        y = mixer.forward(inputs[a:a + n].to(DEV, eng.dtype), batch, eng._views[0]).float()
+        if y.dim() == 3:            # the partial sums of a projection cut along K
+            y = y.sum(dim=0)
+        outs.append(y.cpu())
+        eng.raise_on_status()
+        eng.cache.commit(rid)
+        eng.cache.check_invariants()
+        a += n
+    eng.close(rid)
+    return torch.cat(outs)
+
+
+CUTS = {
+    "whole": lambda T: [T],
+    "one by one": lambda T: [1] * T,
+    "portions": lambda T: _portions(T, (7, 2, 16, 3, 2, 31, 5)),
+    "prompt then decode": lambda T: [T - 20] + [1] * 20,
+}
+
+
+def _portions(T, sizes):
+    out, i = [], 0
+    while sum(out) < T:
+        out.append(min(sizes[i % len(sizes)], T - sum(out)))
+        i += 1
+    return out
+
+
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("width", [30, 64])
+def test_the_gated_recurrence_mixer_however_the_sequence_is_cut(tmp_path, cut, width):
+    eng, cfg, w = _one_layer(tmp_path, mingru(width), 24, "float32", seed=9)
+    T = 75
+    torch.manual_seed(4)
+    x = torch.randn(T, 24)
+    _run(eng, torch.randn(40, 24) * 3.0, [40], rid="earlier")        # the slot's earlier owner leaves its state behind
+    ref = plain.mingru(x.double(), cfg["layers"][0]["mixer"], w, "l0.mix.")
+    got = _run(eng, x, CUTS[cut](T))
+    err = (got.double() - ref).abs().max(dim=1).values
+    assert float(err.max()) < 1e-4, (int(err.argmax()), float(err.max()))
+    x2 = x.clone()
+    x2[30] += 2.0                    # the premise: the state matters ten positions on
+    assert float((plain.mingru(x2.double(), cfg["layers"][0]["mixer"], w, "l0.mix.")[40] - ref[40]).abs().max()) > 1e-4
+
+
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("heads, dim, rank", [(3, 6, 5), (2, 32, 16), (1, 40, 3)])
+def test_the_time_mixing_mixer_however_the_sequence_is_cut(tmp_path, cut, heads, dim, rank):
+    eng, cfg, w = _one_layer(tmp_path, wkv(heads, dim, rank=rank), 24, "float32", seed=10, eps=2e-6)
+    assert eng.model.blocks[0].mixer.w1.out_features == rank
+    T = 75
+    torch.manual_seed(5)
+    x = torch.randn(T, 24)
+    _run(eng, torch.randn(40, 24) * 3.0, [40], rid="earlier")
+    ref = plain.wkv(x.double(), cfg["layers"][0]["mixer"], w, "l0.mix.", 2e-6)
+    got = _run(eng, x, CUTS[cut](T))
+    err = (got.double() - ref).abs().max(dim=1).values
+    assert float(err.max()) < 1e-4, (int(err.argmax()), float(err.max()))
+    # the premises: the state matters twenty positions on, and so does the token before (the shift) and the bonus
+    x2 = x.clone()
+    x2[20] += 1.0
+    assert float((plain.wkv(x2.double(), cfg["layers"][0]["mixer"], w, "l0.mix.", 2e-6)[40] - ref[40]).abs().max()) > 1e-4
+    w2 = dict(w)
+    w2["l0.mix.u"] = torch.zeros_like(w["l0.mix.u"])
+    assert float((plain.wkv(x.double(), cfg["layers"][0]["mixer"], w2, "l0.mix.", 2e-6) - ref).abs().max()) > 1e-2
+
+
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("chunk, taps, page", [(9, 2, 8), (16, 4, 8), (17, 1, 8), (None, 3, 16), (64, None, 16)])
+def test_the_two_branches_however_the_sequence_is_cut(tmp_path, cut, chunk, taps, page):
+    """Attention over chunks of 9, 16, 17 and none over pages of 8 and 16, with convolutions of one to four taps on q, k
+    and v, beside the linear branch. One input is scaled so that its key's score lies far beyond the cap for every row that
+    sees it; it stands at a chunk's LAST position (a page's last row where the chunk is a multiple of the page), so the
+    rows just inside and just outside differ widely."""
+    entry = parallel(left(4, 2, 12, 6, rot_dims=8, chunk=chunk, conv=taps, softcap=6.0, base=200.0), right(3, 5, 7, (0.5, 0.9, 0.97)), 0.8, 1.3)
+    eng, cfg, w = _one_layer(tmp_path, entry, 24, "float32", page_size=page, seed=11, eps=2e-6)
+    T = 75
+    far = 31 if not chunk else (chunk * 3 - 1 if chunk * 3 < T else chunk - 1)
+    torch.manual_seed(6)
+    x = torch.randn(T, 24) * 0.5
+    x[far] *= 8.0
+    _run(eng, torch.randn(40, 24) * 3.0, [40], rid="earlier")
+    m = cfg["layers"][0]["mixer"]
+    ref = plain.parallel_mixer(x.double(), m, w, "l0.mix.", 2e-6)
+    got = _run(eng, x, CUTS[cut](T))
+    err = (got.double() - ref).abs().max(dim=1).values
+    assert float(err.max()) < 1e-4, (int(err.argmax()), float(err.max()))
+    # the premises: the cap, the convolution and the scaled input all matter
+    loose = dict(m, left=dict(m["left"], softcap=None))
+    assert float((plain.parallel_mixer(x.double(), loose, w, "l0.mix.", 2e-6) - ref).abs().max()) > 1e-2
+    x2 = x.clone()
+    x2[far] = 0.0
+    left_ref = plain.conv_attention(x.double(), m["left"], w, "l0.mix.left.")
+    moved = ((plain.conv_attention(x2.double(), m["left"], w, "l0.mix.left.") - left_ref).abs().max(dim=1).values > 0.02).nonzero().flatten().tolist()
+    reach = (taps or 1) - 1       # the convolution carries an input into the next taps - 1 keys
+    last = T - 1 if chunk is None else min(T - 1, (far // chunk + 1) * chunk - 1 + (chunk if reach else 0))
+    assert moved and far in moved and set(moved) <= set(range(far, last + 1))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_branches_far_into_a_sequence(tmp_path, dtype):
+    """Positions beyond a thousand (angles in 32-bit), heads of 64 / 64 (the tensor-core kernel's sizes), a chunk of 80."""
+    entry = parallel(left(4, 1, 64, 64, rot_dims=64, chunk=80, conv=3, softcap=20.0, base=30000.0), right(2, 16, 32, (0.9, 0.99)), 1.2, 0.5)
+    eng, cfg, w = _one_layer(tmp_path, entry, 32, dtype, page_size=16, seed=5, max_tokens=1152)
+    T = 1100
+    torch.manual_seed(6)
+    x = (torch.randn(T, 32) * 0.7).to(torch.bfloat16).float()
+    ref = plain.parallel_mixer(x.double(), cfg["layers"][0]["mixer"], w, "l0.mix.", 1e-6)
+    got = _run(eng, x, [1000, 37] + [1] * 63)
+    err = float((got.double() - ref).abs().max())
+    assert err < (2e-4 if dtype == "float32" else 0.08), err
+
+
+@pytest.mark.parametrize("kind", ["mingru", "wkv", "parallel"])
+def test_a_state_over_three_hundred_single_steps_in_bfloat16(tmp_path, kind):
+    entry = {"mingru": mingru(48), "wkv": wkv(2, 16, rank=8),
+             "parallel": parallel(left(2, 1, 16, 16, rot_dims=16, chunk=32, conv=3, softcap=10.0), right(2, 16, 16, (0.95, 0.999)))}[kind]
+    eng, cfg, w = _one_layer(tmp_path, entry, 32, "bfloat16", seed=10)
+    T = 320
+    torch.manual_seed(5)
+    x = torch.randn(T, 32).to(torch.bfloat16).float()
+    m = cfg["layers"][0]["mixer"]
+    ref = {"mingru": lambda: plain.mingru(x.double(), m, w, "l0.mix."), "wkv": lambda: plain.wkv(x.double(), m, w, "l0.mix.", 1e-6),
+           "parallel": lambda: plain.parallel_mixer(x.double(), m, w, "l0.mix.", 1e-6)}[kind]()
+    got = _run(eng, x, [3] + [1] * (T - 3))
+    whole = _run(eng, x, [T])
+    tol = 0.08 * max(1.0, float(ref.abs().max()) / 4)
+    assert float((got.double() - ref).abs().max()) < tol and float((whole.double() - ref).abs().max()) < tol
+    assert float((got[-50:] - whole[-50:]).abs().max()) < tol       # no drift between the two ways to get there
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("taps", [1, 2, 5])
+def test_the_block_with_its_input_convolution(tmp_path, dtype, taps):
+    """One layer as a whole (norm, input convolution, mixer, feed-forward with the squared relu) through the step
+    function in portions; the stream after the layer against the plain implementation."""
+    from quantinfer_b200.engine import StepEntry
+    from quantinfer_b200.parts.norm import sum_partials
+
+    eng, cfg, w = _one_layer(tmp_path, mingru(20, ff=36), 24, dtype, seed=13, taps=taps)
+    toks = random_tokens(40, 16, seed=2)
+    ref = plain.run_layers(cfg, w, toks)[0]
+    taken = []
+    eng.model.tap = lambda call, resid, delta: taken.append((resid + sum_partials(delta).float()).cpu())
+    eng.open("r")
+    for a, b in ((0, 9), (9, 10), (10, 12), (12, 40)):
+        eng.step([StepEntry("r", toks[a:b], [])])
+    got = torch.cat(taken)
+    assert float((got.double() - ref).abs().max()) < (2e-5 if dtype == "float32" else 0.02) * max(1.0, float(ref.abs().max()))
+
+
+# ---------------------------------------------------------------- whole models, replayed
+
+
+def _family(name, reqs, family):
+    longest = round64(max(LENGTHS[name]))
+    if family == "whole":
+        return whole_trace(reqs), longest
+    if family == "tail":
+        return tail_trace(reqs, 48), longest
+    if family == "portions":
+        return portions_trace(reqs), longest
+    steps, peak = mixed_trace(reqs, seed=5, max_live=4, max_tokens=longest + 2 * 64)
+    assert sum(round64(n) for n in LENGTHS[name]) > peak and max(len(s["entries"]) for s in steps) >= 3
+    return steps, peak
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
+def test_replay_family(models, name, dtype, family):
+    folder, cfg, w = models[name]
+    steps, max_tokens = _family(name, _requests(name), family)
+    got = run_trace_engine(folder, dtype, steps, max_tokens, PAGE_SIZES[name])
+    _compare(got, _expect(models, name), name, dtype, family)
+
+
+def test_the_cuts_agree_with_one_another_in_float32(models):
+    """What a position's logits are must not depend on how its prompt was cut or on its company in the batch."""
+    folder, cfg, w = models["U"]
+    reqs = _requests("U")
+    runs = []
+    for family in ("whole", "tail", "portions", "mixed"):
+        steps, max_tokens = _family("U", reqs, family)
+        runs.append(run_trace_engine(folder, "float32", steps, max_tokens, PAGE_SIZES["U"]))
+    for other in runs[1:]:
+        worst = max(float(np.abs(other[k] - runs[0][k]).max()) for k in runs[0])
+        assert worst <= 2e-5, worst
+
+
+def test_a_stale_state_shows(models):
+    """The premise of the replay tests: a request that takes over a slot without its state being cleared (the manager's
+    zeroing switched off, and the kernels told that the sequence goes on) gives other logits, far beyond the bound."""
+    from quantinfer_b200.engine import Engine, StepEntry
+
+    folder, cfg, w = models["U"]
+    eng = Engine.from_folder(folder, dtype="float32", page_size=8, max_tokens=256, max_requests=1)
+    a, b = random_tokens(40, cfg["vocab"], 1), random_tokens(30, cfg["vocab"], 2)
+    eng.open("a")
+    eng.step([StepEntry("a", a, [])])
+    eng.close("a")
+    eng.open("b")
+    clean_run = eng.step([StepEntry("b", b, [29])]).cpu().clone()
+    eng.close("b")
+    eng.open("a")
+    eng.step([StepEntry("a", a, [])])
+    stale = eng.cache._state_rows.clone()
+    eng.close("a")
+    eng.open("b")
+    eng.step([StepEntry("b", b[:1], [])])
+    eng.cache._state_rows.copy_(stale)             # as if the slot had not been cleared
+    dirty = eng.step([StepEntry("b", b[1:], [28])]).cpu()
+    assert float((dirty - clean_run).abs().max()) > 50 * TOL_F32
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(models, dtype):
+    """bin/trace_run as a child process, the default page size, four slots, a mixed trace in which pages and slots are
+    used again."""
+    import tempfile
+    from pathlib import Path
+
+    folder, cfg, w = models["V"]
+    reqs = _requests("V")
+    steps, peak = mixed_trace(reqs, seed=9, max_live=4, max_tokens=round64(max(LENGTHS["V"])) + 128)
+    with tempfile.TemporaryDirectory() as out:
+        cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", out,
+               "--max-tokens", str(peak)]
+        r = subprocess.run(cmd, input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-3000:]
+        assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+        outputs = {}
+        for s in steps:
+            wanted = sum(len(e["want"]) for e in s["entries"])
+            if wanted:
+                outputs[s["step"]] = np.fromfile(Path(out) / f"{s['step']}.f32", dtype="<f4").reshape(wanted, cfg["vocab"])
+    _compare(collect(steps, outputs), _expect(models, "V"), "V", dtype, "trace_run")
+
+
+# ---------------------------------------------------------------- generation through the scheduler
+
+
+def _plain_greedy(cfg, w, prompt, n_new):
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(plain.forward(cfg, w, toks)[-1].argmax()))
+    return toks[len(prompt):]
+
+
+@pytest.mark.parametrize("name, run_ahead, graphs", [("U", True, True), ("W", False, True), ("V", True, False)])
+def test_greedy_generation_through_the_scheduler(models, name, run_ahead, graphs):
+    """Three prompts of unequal length taken in portions of five tokens while earlier ones already decode, decode
+    steps replayed from CUDA graphs and launched ahead of the host: the plain implementation's tokens."""
+    import quantinfer_b200 as q
+    from quantinfer_b200.engine import Engine
+
+    folder, cfg, w = models[name]
+    prompts = [random_tokens(n, cfg["vocab"], seed=n) for n in (13, 1, 27)]
+    eng = Engine.from_folder(folder, dtype="float32", page_size=PAGE_SIZES[name], max_tokens=512, max_requests=4, use_graphs=graphs)
+    model_ = q.Model.from_engine(eng, max_batch_tokens=16, chunk_size=5, run_ahead=run_ahead)
+    got = model_.generate_batch(prompts, max_new_tokens=10, eos_token_id=None)
+    for p, g in zip(prompts, got):
+        assert g == _plain_greedy(cfg, w, p, 10), (name, len(p))
+    # again on the same engine: slots and pages of the first call are used again, state must start afresh
+    assert model_.generate_batch(prompts[::-1], max_new_tokens=10, eos_token_id=None) == got[::-1]
+    assert model_.generate_tokens(prompts[2], max_new_tokens=10, eos_token_id=None) == got[2]
+
+
+def test_command_line_generates_the_same_tokens(models):
+    folder, cfg, w = models["W"]
+    prompt = random_tokens(9, cfg["vocab"], seed=1)
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "quantinfer"), "generate", "--input", str(folder), "--tokens",
+                        ",".join(map(str, prompt)), "--max-new-tokens", "10", "--dtype", "float32", "--page-size", "8"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("generated_tokens=")][0]
+    assert json.loads(line.split("=", 1)[1]) == _plain_greedy(cfg, w, prompt, 10)
+
+
+def test_random_weights_from_the_command_line(tmp_path):
+    """`--random-weights` draws a model of this design from its config.json alone (the decay's rank is free there)."""
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(clean(CONFIGS["U"])))
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "quantinfer"), "generate", "--input", str(cfg), "--random-weights", "--tokens",
+                        "1,2,3", "--max-new-tokens", "5", "--page-size", "8"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert len(json.loads([l for l in r.stdout.splitlines() if l.startswith("generated_tokens=")][0].split("=", 1)[1])) == 5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_past_chunks_and_pages(models, dtype):
+    """Three tokens of prompt, then a hundred and fifty decoded one by one with given ids: every chunk's edge is
+    crossed by decoded tokens, pages fill and go back, the recurrent layers' state is carried through every step."""
+    folder, cfg, w = models["U"]
+    toks = random_tokens(153, cfg["vocab"], seed=8)
+    steps = tail_trace({"long": toks}, 150)
+    got = run_trace_engine(folder, dtype, steps, 192, PAGE_SIZES["U"])
+    _compare(got, plain_rows(cfg, w, {"long": toks}), "U", dtype, "long decode")
