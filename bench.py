@@ -201,10 +201,53 @@ def kiruvik_arithmetic(config, spec):
     return a
 
 
+def dulotar_arithmetic(config, spec):
+    """The same for a model of the Dulotar design: per layer call the mixer's projections, the dense feed-forward's two
+    matrices, attention over the keys of the query's chunk, and the recurrences' multiply-adds (gated recurrence: a few a
+    channel; matrix states: three a state element) with the 32-bit state they read and write in a decode step."""
+    H, V = spec.hidden_size, spec.vocab_size
+    params = kv = scan_flops = state_bytes = 0
+    chunks = []
+    taps = config.canon_taps or 0
+    for layer in config.layers:
+        m = layer.mixer
+        state_bytes += 2 * 4 * max(taps - 1, 0) * H
+        if layer.kind == "parallel":
+            l, r = m.left, m.right
+            qkv = (l.heads + l.kv_heads) * l.dim + l.kv_heads * l.vdim
+            params += H * qkv + l.heads * l.vdim * H + H * (2 * r.heads * r.dim + 2 * r.heads * r.vdim) + r.heads * r.vdim * H
+            kv += 2 * l.kv_heads * (l.dim + l.vdim)
+            chunks.append((l.heads, l.dim, l.vdim, l.kv_heads, l.chunk))
+            scan_flops += 4.0 * r.heads * r.dim * r.vdim
+            state_bytes += 2 * 4 * (r.heads * r.dim * r.vdim + max((l.conv or 1) - 1, 0) * qkv)
+        elif layer.kind == "mingru":
+            params += 4 * H * m.width
+            scan_flops += 8.0 * m.width
+            state_bytes += 2 * 4 * m.width
+        else:
+            inner, rank = m.heads * m.dim, 16
+            params += 5 * H * inner + rank * (H + inner)
+            scan_flops += 6.0 * inner * m.dim
+            state_bytes += 2 * 4 * (inner * m.dim + H)
+        if layer.ff is not None:
+            params += 2 * H * layer.ff
+    a = dict(L=len(config.layers), H=H, V=V, layer_params=params / len(config.layers), stored_params=params)
+    a["weight_bytes"] = 2 * (params + V * H)
+    a["kv_bytes_per_token"] = 0
+    a["kv_bytes"] = lambda ctx: sum(2 * g * (d + dv) * (min(ctx, ctx % c + 1) if c else ctx) for _, d, dv, g, c in chunks)
+    a["state_bytes"] = state_bytes
+    a["gemm_flops"] = lambda T, rows_=1: 2.0 * T * params + 2.0 * H * V * rows_
+    a["attn_flops"] = lambda T: sum(2.0 * h * (d + dv) * sum((t % c if c else t) + 1 for t in range(T)) for h, d, dv, _, c in chunks)
+    a["scan_flops"] = lambda T: scan_flops * T
+    return a
+
+
 def model_arithmetic(config, spec):
     """Parameter counts, bytes and flops of the configuration (every matrix bf16)."""
     if type(config).__name__ == "KiruvikConfig":
         return kiruvik_arithmetic(config, spec)
+    if type(config).__name__ == "DulotarConfig":
+        return dulotar_arithmetic(config, spec)
     if hasattr(config, "layers"):
         return latent_arithmetic(config, spec)
     L, H, I, V = len(spec.layers), spec.hidden_size, config.intermediate_size, spec.vocab_size
@@ -514,7 +557,45 @@ def kiruvik_entries(size):
     return (dict(common, config=new, name=f"Kiruvik layers of width {size}"), dict(common, config=dense, name=f"Qwen3 layers of width {size}"))
 
 
-def compare_kiruvik(args):
+# ---- the Dulotar design beside Kiruvik layers of equal width --------------------------------------------------------
+# (width, softmax heads / kv heads of 128, dense feed-forward, linear-attention heads of 64 x 128, gated recurrence width,
+# time-mixing heads of 64): four layers, two branches + dense, gated recurrence, time mixing, two branches + dense; beside
+# them the closest existing design, Kiruvik, as attention + dense, state-space, state-space, attention + dense
+DULOTAR_SIZES = {
+    "2048": dict(width=2048, heads=16, kv=4, ff=8192, lheads=16, gru=4096, wheads=32, sheads=64),
+    "4096": dict(width=4096, heads=32, kv=8, ff=12288, lheads=32, gru=8192, wheads=64, sheads=128),
+}
+
+
+def dulotar_entries(size):
+    z = DULOTAR_SIZES[size]
+    both = {"left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4, "softcap": 50.0,
+                     "rot": {"base": 500000.0, "dims": 64}, "mask": {"size": KIRUVIK_CHUNK}},
+            "right": {"heads": z["lheads"], "dim": 64, "vdim": 128, "decay": [1.0 - 2.0 ** -(2 + 6 * i / z["lheads"]) for i in range(z["lheads"])]},
+            "left_scale": 1.0, "right_scale": 0.5}
+    den = {"kind": "dense", "ff": z["ff"]}
+    layers = [{"type": "parallel", "mixer": both, "mlp": den}, {"type": "mingru", "mixer": {"width": z["gru"]}, "mlp": None},
+              {"type": "wkv", "mixer": {"heads": z["wheads"], "dim": 64}, "mlp": None}, {"type": "parallel", "mixer": both, "mlp": den}]
+    new = dict(architecture="Dulotar", vocab=COMPARE_VOCAB, width=z["width"], norm={"eps": 1e-5}, embedding={"scale": 1.0},
+               canon={"taps": 4}, layers=layers)
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+           "rot": {"base": 500000.0, "dims": 64}, "mask": {"size": KIRUVIK_CHUNK}}
+    rec = {"heads": z["sheads"], "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+    old = dict(architecture="Kiruvik", vocab=COMPARE_VOCAB, width=z["width"], norm={"eps": 1e-6}, residual_mult=0.6,
+               layers=[{"type": "attention", "mixer": att, "mlp": den}, {"type": "mamba2", "mixer": rec, "mlp": None},
+                       {"type": "mamba2", "mixer": rec, "mlp": None}, {"type": "attention", "mixer": att, "mlp": den}])
+    common = dict(seed=5, prompt_len=COMPARE_PROMPT, context=4096, batch=COMPARE_BATCH, points=())
+    return (dict(common, config=new, name=f"Dulotar layers of width {size}"), dict(common, config=old, name=f"Kiruvik layers of width {size}"))
+
+
+def compare_dulotar(args):
+    """Prefill and decode throughput of four Dulotar layers (softmax + linear attention side by side, a gated recurrence,
+    time mixing, dense feed-forwards) beside four Kiruvik layers of the same width (attention and state-space mixers, dense
+    feed-forwards), and each kernel class of both alone with its share of the roofline."""
+    return compare_kiruvik(args, "Dulotar layers beside Kiruvik layers of equal width", DULOTAR_SIZES, dulotar_entries)
+
+
+def compare_kiruvik(args, title="Kiruvik layers beside dense GQA (Qwen3) layers of equal width", sizes=None, entries_of=None):
     """Prefill and decode throughput of four Kiruvik layers (attention and state-space mixers, dense and routed
     feed-forwards) beside four dense GQA layers of the same width, heads and vocabulary, and each kernel class of both
     alone (the others left out of the step) with its share of the roofline."""
@@ -525,12 +606,13 @@ def compare_kiruvik(args):
     from quantinfer_b200 import kernels
 
     hbm, sustained, burst, src = peaks()
-    out = {"compare": "Kiruvik layers beside dense GQA (Qwen3) layers of equal width", "layers": COMPARE_LAYERS, "vocab": COMPARE_VOCAB,
+    sizes, entries_of = sizes or KIRUVIK_SIZES, entries_of or kiruvik_entries
+    out = {"compare": title, "layers": COMPARE_LAYERS, "vocab": COMPARE_VOCAB,
            "prompt": COMPARE_PROMPT, "decode_batch": COMPARE_BATCH, "chunk": KIRUVIK_CHUNK, "peaks": src, "sizes": {}}
     every = ("gemm", "attention", "norm", "rope", "scan", "other")
-    for size in (args.compare_sizes.split(",") if args.compare_sizes else list(KIRUVIK_SIZES)):
+    for size in (args.compare_sizes.split(",") if args.compare_sizes else list(sizes)):
         rows = {}
-        for entry in kiruvik_entries(size):
+        for entry in entries_of(size):
             args.batch = COMPARE_BATCH
             bench = Bench(args, entry)
             a, T = bench.arith, bench.prompt_len
@@ -848,7 +930,7 @@ def main() -> int:
                     help="run one part only (for profiler captures of a small case)")
     ap.add_argument("--timeline", action="store_true",
                     help="build the kernels with their time stamps and print where a decode step's time goes, kernel by kernel")
-    ap.add_argument("--compare", nargs="?", const="bebuvik", default=None, choices=["bebuvik", "kiruvik"],
+    ap.add_argument("--compare", nargs="?", const="bebuvik", default=None, choices=["bebuvik", "kiruvik", "dulotar"],
                     help="instead of the headline workload: layers of another design (default: the latent-attention design) "
                          "beside dense GQA layers of equal sizes")
     ap.add_argument("--compare-sizes", default=None, help="widths to compare, with commas between them (default: all)")
@@ -877,7 +959,8 @@ def main() -> int:
     torch.cuda.set_device(0)
     if args.compare:
         args.skip_points = args.skip_classes = True
-        print(json.dumps(compare_kiruvik(args) if args.compare == "kiruvik" else compare_designs(args)))
+        run = {"kiruvik": compare_kiruvik, "dulotar": compare_dulotar, "bebuvik": compare_designs}[args.compare]
+        print(json.dumps(run(args)))
         return 0
     if args.only == "mixed":
         print(json.dumps({"only": "mixed", "mixed": mixed_workload(args, entry)}))
