@@ -263,7 +263,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                       const int* __restrict__ tile_req, const int* __restrict__ tile_q0, int nq, int nkv,
                                       float scale_log2e, int window, int* __restrict__ status, int n_ranges,
                                       float* __restrict__ ws_o, float* __restrict__ ws_ml, int chunk,
-                                      const qi::bf16* __restrict__ gate, long long ldg) {
+                                      const qi::bf16* __restrict__ gate, long long ldg, float cap, float cap_pre,
+                                      float out_scale) {
     extern __shared__ uint8_t smem_raw[];
     using B = Bars;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -480,6 +481,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + B::s_free);
+            if (cap > 0.f) {
+                // soft cap: a score s becomes cap tanh(s scale / cap), with tanh(x) = 1 - 2 / (1 + e^(2x)); scale_log2e is
+                // then the base-2 factor alone
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    const float t = ex2(__uint_as_float(sv[c]) * cap_pre);
+                    sv[c] = __float_as_uint(fmaf(-cap, __fdividef(2.f, 1.f + t), cap));
+                }
+            }
             // a tile that lies wholly inside every row's span takes the code without the comparisons
             const bool interior = __all_sync(0xffffffffu, c_lo == 0 && c_hi == BN);
             const float mx = interior ? row_max<false>(sv, 0, BN) : row_max<true>(sv, c_lo, c_hi);
@@ -543,7 +553,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
         } else if (ok) {
             tc_fence_after();
-            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const float inv = l > 0.f ? out_scale / l : 0.f;
             qi::bf16* orow = out + ((size_t)(q0 + row) * nq + h) * D;
             const qi::bf16* grow = gate ? gate + (size_t)(q0 + row) * ldg + (size_t)h * D : nullptr;
             // the row's 128 columns in two halves, each half's loads in flight together
@@ -585,7 +595,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 // out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M) over the key ranges of a query row, in range order.
 __global__ void attention_prefill_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                                qi::bf16* __restrict__ out, int nq, int n_ranges,
-                                               const qi::bf16* __restrict__ gate, long long ldg) {
+                                               const qi::bf16* __restrict__ gate, long long ldg, float out_scale) {
     qi::pdl_enter();
     const int h = blockIdx.x;
     const size_t t = blockIdx.y;
@@ -601,7 +611,7 @@ __global__ void attention_prefill_merge_kernel(const float* __restrict__ ws_o, c
             L += ws_ml[(base + s) * 2 + 1] * f;
             O += ws_o[(base + s) * D + col] * f;
         }
-        float o = L > 0.f ? O / L : 0.f;
+        float o = L > 0.f ? O / L * out_scale : 0.f;
         if (gate) o = o / (1.f + __expf(-__bfloat162float(gate[t * (size_t)ldg + (size_t)h * D + col])));
         out[(t * nq + h) * D + col] = __float2bfloat16_rn(o);
     }
@@ -654,13 +664,16 @@ extern "C" int qi_attention_prefill_tcgen05_supported(int nq, int nkv, int d, in
 // cuts every query tile's keys into that many ranges over separate CTAs, merged by a second kernel;
 // `workspace` must then hold n_tokens * nq * n_ranges * (128 + 2) floats. chunk > 0: a query at position i sees
 // key j <= i only if floor(i / chunk) = floor(j / chunk). gate (or null): bfloat16 [n_tokens, nq * 128] with rows
-// `ldg` elements apart; the output is multiplied element by element with its sigmoid.
+// `ldg` elements apart; the output is multiplied element by element with its sigmoid. softcap c > 0: a score s (scale
+// applied) becomes c tanh(s / c) before the softmax. out_scale multiplies the result.
 extern "C" int qi_attention_prefill_tcgen05_ex(const void* q, void* out, const void* k_pages, const void* v_pages,
                                                const int* block_table, int max_blocks, int page_size, int num_pages,
                                                const int* q_start, const int* start_pos, const int* tile_req,
                                                const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int d,
                                                float scale, int window, int chunk, const void* gate, long long ldg,
-                                               int n_ranges, float* workspace, int* status, cudaStream_t stream) {
+                                               int n_ranges, float* workspace, int* status, float softcap, float out_scale,
+                                               cudaStream_t stream) {
+    QI_REQUIRE(softcap >= 0.f && scale > 0.f, "attention_prefill_tcgen05: the soft cap must be >= 0 (0 = none) and the scale positive");
     QI_REQUIRE(chunk >= 0 && (!gate || (((uintptr_t)gate & 15) == 0 && ldg % 8 == 0 && ldg >= (long long)nq * D)),
                "attention_prefill_tcgen05: a gate must be 16-byte aligned with rows a multiple of 8 elements apart");
     QI_REQUIRE(qi_attention_prefill_tcgen05_supported(nq, nkv, d, page_size, max_blocks),
@@ -687,14 +700,17 @@ extern "C" int qi_attention_prefill_tcgen05_ex(const void* q, void* out, const v
     if (make_map(&mv, v_pages, (long long)num_pages * nkv * page_size, D, box_rows)) return 1;
     float* ws_o = workspace;
     float* ws_ml = workspace ? workspace + (size_t)n_tokens * nq * n_ranges * D : nullptr;
+    // with a cap the kernel sees e^(2 s scale / cap) as a power of two, and the capped score needs the base-2 factor alone
+    const float log2e = 1.4426950408889634f;
+    const float cap_pre = softcap > 0.f ? 2.f * log2e * scale / softcap : 0.f;
     qi::launch(attention_prefill_tcgen05_kernel, dim3(nq, n_tiles, n_ranges), dim3(kThreads), kSmemBytes, stream, mq, mk, mv,
                (qi::bf16*)out, block_table, max_blocks, page_size, box_rows, num_pages, q_start, start_pos, tile_req,
-               tile_q0, nq, nkv, scale * 1.4426950408889634f, window, status, n_ranges, ws_o, ws_ml, chunk,
-               (const qi::bf16*)gate, ldg);
+               tile_q0, nq, nkv, softcap > 0.f ? log2e : scale * log2e, window, status, n_ranges, ws_o, ws_ml, chunk,
+               (const qi::bf16*)gate, ldg, softcap, cap_pre, out_scale);
     if (n_ranges > 1) {
         if (int rc = qi::check_launch("attention_prefill_tcgen05")) return rc;
         qi::launch(attention_prefill_merge_kernel, dim3(nq, n_tokens), dim3(128), 0, stream, (const float*)ws_o,
-                   (const float*)ws_ml, (qi::bf16*)out, nq, n_ranges, (const qi::bf16*)gate, ldg);
+                   (const float*)ws_ml, (qi::bf16*)out, nq, n_ranges, (const qi::bf16*)gate, ldg, out_scale);
         return qi::check_launch("attention_prefill_merge");
     }
     return qi::check_launch("attention_prefill_tcgen05");
@@ -708,7 +724,7 @@ extern "C" int qi_attention_prefill_tcgen05(const void* q, void* out, const void
                                             cudaStream_t stream) {
     return qi_attention_prefill_tcgen05_ex(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start,
                                            start_pos, tile_req, tile_q0, n_tiles, n_tokens, nq, nkv, d, scale, window, 0,
-                                           nullptr, 0, n_ranges, workspace, status, stream);
+                                           nullptr, 0, n_ranges, workspace, status, 0.f, 1.f, stream);
 }
 
 QI_TL_EXPORT(qi_timeline_prefill_attention)

@@ -30,6 +30,7 @@ __device__ __forceinline__ float siluf_(float x) { return x / (1.0f + expf(-x));
 
 constexpr int kGruLanes = 32;      // channels a block
 constexpr int kGruMaxSlices = 32;
+constexpr int kGruAhead = 8;       // tokens whose rows a thread fetches together
 
 template <typename T, typename TO>
 __global__ void __launch_bounds__(kGruLanes * kGruMaxSlices)
@@ -48,16 +49,28 @@ mingru_scan_kernel(const T* __restrict__ proj, long long ldp, const float* __res
     const float bzc = live ? bz[c] : 0.f, bxc = live ? bx[c] : 0.f;
     float* st = state + (size_t)slot_ids[e] * state_stride + c;
     float S = 0.f;
+    // tokens run in groups of kGruAhead whose rows are fetched together, ahead of the arithmetic that depends on S
     if (slices > 1) {
         float a = 1.f, b = 0.f;
         if (live) {
-            for (int t = t0; t < t1; ++t) {
-                const T* row = proj + (size_t)(first + t) * ldp;
-                const float z = sigmoidf_(qi::to_f32<T>(row[c]) + bzc);
-                const float u = qi::to_f32<T>(row[width + c]) + bxc;
-                const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
-                a *= 1.f - z;
-                b = fmaf(1.f - z, b, z * cand);
+            for (int t = t0; t < t1; t += kGruAhead) {
+                float pz[kGruAhead], px[kGruAhead];
+#pragma unroll
+                for (int i = 0; i < kGruAhead; ++i) {
+                    const T* row = proj + (size_t)(first + min(t + i, t1 - 1)) * ldp;
+                    pz[i] = qi::to_f32<T>(row[c]);
+                    px[i] = qi::to_f32<T>(row[width + c]);
+                }
+#pragma unroll
+                for (int i = 0; i < kGruAhead; ++i) {
+                    if (t + i < t1) {
+                        const float z = sigmoidf_(pz[i] + bzc);
+                        const float u = px[i] + bxc;
+                        const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+                        a *= 1.f - z;
+                        b = fmaf(1.f - z, b, z * cand);
+                    }
+                }
             }
         }
         sh_a[sl][threadIdx.x] = a;
@@ -67,13 +80,25 @@ mingru_scan_kernel(const T* __restrict__ proj, long long ldp, const float* __res
     if (!live) return;
     S = start_pos[e] > 0 ? *st : 0.f;
     for (int s = 0; s < sl; ++s) S = fmaf(sh_a[s][threadIdx.x], S, sh_b[s][threadIdx.x]);
-    for (int t = t0; t < t1; ++t) {
-        const T* row = proj + (size_t)(first + t) * ldp;
-        const float z = sigmoidf_(qi::to_f32<T>(row[c]) + bzc);
-        const float u = qi::to_f32<T>(row[width + c]) + bxc;
-        const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
-        S = fmaf(1.f - z, S, z * cand);
-        out[(size_t)(first + t) * width + c] = qi::from_f32<TO>(S * siluf_(qi::to_f32<T>(row[2 * width + c])));
+    for (int t = t0; t < t1; t += kGruAhead) {
+        float pz[kGruAhead], px[kGruAhead], pg[kGruAhead];
+#pragma unroll
+        for (int i = 0; i < kGruAhead; ++i) {
+            const T* row = proj + (size_t)(first + min(t + i, t1 - 1)) * ldp;
+            pz[i] = qi::to_f32<T>(row[c]);
+            px[i] = qi::to_f32<T>(row[width + c]);
+            pg[i] = qi::to_f32<T>(row[2 * width + c]);
+        }
+#pragma unroll
+        for (int i = 0; i < kGruAhead; ++i) {
+            if (t + i < t1) {
+                const float z = sigmoidf_(pz[i] + bzc);
+                const float u = px[i] + bxc;
+                const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+                S = fmaf(1.f - z, S, z * cand);
+                out[(size_t)(first + t + i) * width + c] = qi::from_f32<TO>(S * siluf_(pg[i]));
+            }
+        }
     }
     // the slice that holds the entry's last token keeps the state (slices behind it are empty and carry the same value)
     if (sl == slices - 1) *st = S;
@@ -81,32 +106,51 @@ mingru_scan_kernel(const T* __restrict__ proj, long long ldp, const float* __res
 
 // ---------------------------------------------------------------------------------------------------
 // Token shift: out_s[t] = h[t] + (h[t - 1] - h[t]) * mu_s for s = 0 .. n_mix - 1, h[-1] of an entry's first token
-// from the state (the last input of the request's step before; zeros at a sequence's start). One thread per
-// (token, channel); the thread of an entry's first token reads the old state and then writes the entry's last
-// input into it, so the state is read and written by one thread in program order.
+// from the state (the last input of the request's step before; zeros at a sequence's start). One thread per token and
+// VEC neighbouring channels (16 bytes where the row length allows); the thread of an entry's first token reads the old
+// state and then writes the entry's last input into it, so the state is read and written by one thread in program order.
 
-template <typename T>
+template <typename T, int VEC>
+struct alignas(sizeof(T) * VEC) ShiftPack { T v[VEC]; };
+
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 token_shift_kernel(const T* __restrict__ h, const float* __restrict__ mu, float* __restrict__ state, long long state_stride,
                    T* __restrict__ out, const int* __restrict__ token_req, const int* __restrict__ q_start,
                    const int* __restrict__ start_pos, const int* __restrict__ slot_ids, int n_tokens, int C, int n_mix) {
+    using Pack = ShiftPack<T, VEC>;
     qi::pdl_wait();
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)n_tokens * C) return;
-    const int t = (int)(idx / C), c = (int)(idx % C);
+    const int per_row = C / VEC;
+    const size_t item = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= (size_t)n_tokens * per_row) return;
+    const int t = (int)(item / per_row), c = (int)(item % per_row) * VEC;
+    const size_t idx = (size_t)t * C + c;
     const int e = token_req[t];
     const int first = q_start[e];
-    const float x = qi::to_f32<T>(h[idx]);
-    float prev;
+    const Pack xp = *reinterpret_cast<const Pack*>(h + idx);
+    float x[VEC], d[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) x[i] = qi::to_f32<T>(xp.v[i]);
     if (t > first) {
-        prev = qi::to_f32<T>(h[idx - C]);
+        const Pack pp = *reinterpret_cast<const Pack*>(h + idx - C);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) d[i] = qi::to_f32<T>(pp.v[i]) - x[i];
     } else {
         float* st = state + (size_t)slot_ids[e] * state_stride + c;
-        prev = start_pos[e] > 0 ? *st : 0.f;
-        *st = qi::to_f32<T>(h[(size_t)(q_start[e + 1] - 1) * C + c]);
+        const bool carried = start_pos[e] > 0;
+        const Pack lp = *reinterpret_cast<const Pack*>(h + (size_t)(q_start[e + 1] - 1) * C + c);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            d[i] = (carried ? st[i] : 0.f) - x[i];
+            st[i] = qi::to_f32<T>(lp.v[i]);
+        }
     }
-    const float d = prev - x;
-    for (int s = 0; s < n_mix; ++s) out[(size_t)s * n_tokens * C + idx] = qi::from_f32<T>(fmaf(d, mu[(size_t)s * C + c], x));
+    for (int s = 0; s < n_mix; ++s) {
+        Pack op;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) op.v[i] = qi::from_f32<T>(fmaf(d[i], mu[(size_t)s * C + c + i], x[i]));
+        *reinterpret_cast<Pack*>(out + (size_t)s * n_tokens * C + idx) = op;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -116,20 +160,31 @@ token_shift_kernel(const T* __restrict__ h, const float* __restrict__ mu, float*
 //   mode 1 (one decay a head, silu inputs):  S_t = lambda S_(t-1) + k_t v_t^T ;  o_t = S_t^T q_t ;  q, k, v = silu of the projections
 // A block owns one entry, one head and up to kColThreads value columns; thread j keeps column j of S in registers
 // (DK numbers, dk padded with zeros). The operands of kStage tokens are staged in shared memory at a time (decays and
-// activations are evaluated there, once a token and channel); in the inner loop every thread reads them as broadcasts.
-// The state of a slot is laid out [heads, dv, dk], dk fastest.
+// activations are evaluated there, once a token and channel: thread x stages key channels x, x + kColThreads, ...); in
+// the inner loop every thread reads them as broadcasts. The state of a slot is laid out [heads, dv, dk], dk fastest.
+//
+// The recurrence is linear in S, so long entries are cut into segments that run side by side, as three launches:
+// every segment as an entry of its own from zeros, without outputs (o null), leaving its own contribution in a
+// scratch row and the product of its decays per key channel in `decay_out`; matrix_state_chain_kernel, which walks an
+// entry's segments in order, replaces each contribution by the state its segment starts from and moves the request's
+// state to the entry's end; every segment again from that start, now with outputs (write_state 0).
 
 constexpr int kColThreads = 64;
-constexpr int kStage = 8;
 
 template <typename T, int DK, int MODE>
 __global__ void __launch_bounds__(kColThreads)
 matrix_state_scan_kernel(const T* __restrict__ r, long long ldr, const T* __restrict__ k, long long ldk, const T* __restrict__ v,
                          long long ldv, const T* __restrict__ lw, long long ldw, const float* __restrict__ w0,
                          const float* __restrict__ u, const float* __restrict__ lambda, float* __restrict__ state,
-                         long long state_stride, float* __restrict__ o, const int* __restrict__ q_start,
-                         const int* __restrict__ start_pos, const int* __restrict__ slot_ids, int heads, int dk, int dv) {
-    __shared__ float s_r[kStage][DK], s_k[kStage][DK], s_w[kStage][DK], s_v[kStage][kColThreads], s_bonus[kStage];
+                         long long state_stride, float* __restrict__ o, float* __restrict__ decay_out, int write_state,
+                         const int* __restrict__ q_start, const int* __restrict__ start_pos, const int* __restrict__ slot_ids,
+                         int heads, int dk, int dv) {
+    constexpr int kOwn = (DK + kColThreads - 1) / kColThreads;     // key channels a thread stages
+    static_assert(DK % 4 == 0, "the staged operands are read four at a time");
+    constexpr int kStage = DK <= 64 ? 8 : 4;                       // tokens a stage
+    constexpr int kBonusLanes = kColThreads / kStage;              // threads that share a token's bonus sum
+    __shared__ __align__(16) float s_r[kStage][DK], s_k[kStage][DK], s_w[kStage][DK];
+    __shared__ float s_v[kStage][kColThreads], s_bonus[kStage], s_u[MODE == 0 ? DK : 1];
     qi::pdl_wait();
     const int hd = blockIdx.x, e = blockIdx.y;
     const int j = blockIdx.z * kColThreads + threadIdx.x;
@@ -144,69 +199,203 @@ matrix_state_scan_kernel(const T* __restrict__ r, long long ldr, const T* __rest
         for (int i = 0; i < DK; ++i) if (i < dk) S[i] = st[i];
     }
     const float lam = MODE == 1 ? lambda[hd] : 0.f;
+    float w0r[kOwn], dsum[kOwn];        // dsum: minus the logarithm of the product of this entry's decays
+#pragma unroll
+    for (int m = 0; m < kOwn; ++m) {
+        const int i = threadIdx.x + m * kColThreads;
+        const bool in = MODE == 0 && i < dk;
+        w0r[m] = in ? w0[(size_t)hd * dk + i] : 0.f;
+        dsum[m] = 0.f;
+    }
+    if (MODE == 0)
+        for (int i = threadIdx.x; i < DK; i += kColThreads) s_u[i] = i < dk ? u[(size_t)hd * dk + i] : 0.f;
+    // A stage's numbers are fetched into registers one stage ahead, while the stage before is worked through.
+    T f_r[kOwn][kStage], f_k[kOwn][kStage], f_w[MODE == 0 ? kOwn : 1][kStage], f_v[kStage];
+    auto fetch = [&](int base) {
+        const int nt = min(kStage, len - base);
+#pragma unroll
+        for (int m = 0; m < kOwn; ++m) {
+            const int i = threadIdx.x + m * kColThreads;
+            const bool in = i < dk;
+#pragma unroll
+            for (int tt = 0; tt < kStage; ++tt) {
+                if (in && tt < nt) {
+                    const size_t row = (size_t)(first + base + tt);
+                    f_r[m][tt] = r[row * ldr + (size_t)hd * dk + i];
+                    f_k[m][tt] = k[row * ldk + (size_t)hd * dk + i];
+                    if (MODE == 0) f_w[m][tt] = lw[row * ldw + (size_t)hd * dk + i];
+                }
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < kStage; ++tt)
+            if (live && tt < nt) f_v[tt] = v[(size_t)(first + base + tt) * ldv + (size_t)hd * dv + j];
+    };
+    if (len > 0) fetch(0);
     for (int base = 0; base < len; base += kStage) {
         const int nt = min(kStage, len - base);
         __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * DK; idx += kColThreads) {
-            const int tt = idx / DK, i = idx % DK;
-            const size_t row = (size_t)(first + base + tt);
-            float rv = 0.f, kv = 0.f, wv = 0.f;
-            if (i < dk) {
-                rv = qi::to_f32<T>(r[row * ldr + (size_t)hd * dk + i]);
-                kv = qi::to_f32<T>(k[row * ldk + (size_t)hd * dk + i]);
-                if (MODE == 0) {
-                    wv = expf(-expf(qi::to_f32<T>(lw[row * ldw + (size_t)hd * dk + i]) + w0[(size_t)hd * dk + i]));
-                } else {
-                    rv = siluf_(rv);
-                    kv = siluf_(kv);
+#pragma unroll
+        for (int m = 0; m < kOwn; ++m) {
+            const int i = threadIdx.x + m * kColThreads;
+            if (i < DK) {
+                const bool in = i < dk;
+#pragma unroll
+                for (int tt = 0; tt < kStage; ++tt) {
+                    if (tt < nt) {
+                        float rv = 0.f, kv = 0.f, wv = 0.f;
+                        if (in) {
+                            rv = qi::to_f32<T>(f_r[m][tt]);
+                            kv = qi::to_f32<T>(f_k[m][tt]);
+                            if (MODE == 0) {
+                                const float rate = expf(qi::to_f32<T>(f_w[m][tt]) + w0r[m]);
+                                wv = expf(-rate);
+                                dsum[m] += rate;
+                            } else {
+                                rv = siluf_(rv);
+                                kv = siluf_(kv);
+                            }
+                        }
+                        s_r[tt][i] = rv;
+                        s_k[tt][i] = kv;
+                        if (MODE == 0) s_w[tt][i] = wv;
+                    }
                 }
             }
-            s_r[tt][i] = rv;
-            s_k[tt][i] = kv;
-            if (MODE == 0) s_w[tt][i] = wv;
         }
-        for (int idx = threadIdx.x; idx < nt * kColThreads; idx += kColThreads) {
-            const int tt = idx / kColThreads, jj = blockIdx.z * kColThreads + idx % kColThreads;
-            float vv = 0.f;
-            if (jj < dv) {
-                vv = qi::to_f32<T>(v[(size_t)(first + base + tt) * ldv + (size_t)hd * dv + jj]);
+#pragma unroll
+        for (int tt = 0; tt < kStage; ++tt) {
+            if (tt < nt) {
+                float vv = live ? qi::to_f32<T>(f_v[tt]) : 0.f;
                 if (MODE == 1) vv = siluf_(vv);
+                s_v[tt][threadIdx.x] = vv;
             }
-            s_v[tt][idx % kColThreads] = vv;
         }
-        if (MODE == 0) {
+        if (base + kStage < len) fetch(base + kStage);
+        if (MODE == 0 && o) {
             __syncthreads();
-            if (threadIdx.x < nt) {     // the bonus of the current token: sum_i r_i u_i k_i, in the order of i
-                float b = 0.f;
-                for (int i = 0; i < dk; ++i) b = fmaf(s_r[threadIdx.x][i] * u[(size_t)hd * dk + i], s_k[threadIdx.x][i], b);
-                s_bonus[threadIdx.x] = b;
-            }
+            // the bonus of the current token, sum_i r_i u_i k_i: kBonusLanes threads a token, each every kBonusLanes-th channel
+            const int tt = threadIdx.x / kBonusLanes, sub = threadIdx.x % kBonusLanes;
+            float b = 0.f;
+            if (tt < nt)
+                for (int i = sub; i < DK; i += kBonusLanes) b = fmaf(s_r[tt][i] * s_u[i], s_k[tt][i], b);
+#pragma unroll
+            for (int d = kBonusLanes / 2; d > 0; d >>= 1) b += __shfl_xor_sync(0xffffffffu, b, d);
+            if (sub == 0) s_bonus[tt] = b;
         }
         __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {
-            const float vj = s_v[tt][threadIdx.x];
-            float acc = 0.f;
-            if (MODE == 0) {
+        // every thread reads the staged operands as broadcasts, four key channels an instruction
+        if (!o) {                       // a segment's own contribution only
+            for (int tt = 0; tt < nt; ++tt) {
+                const float vj = s_v[tt][threadIdx.x];
+                const float4* k4 = reinterpret_cast<const float4*>(s_k[tt]);
+                const float4* w4 = reinterpret_cast<const float4*>(s_w[tt]);
 #pragma unroll
-                for (int i = 0; i < DK; ++i) {
-                    acc = fmaf(s_r[tt][i], S[i], acc);
-                    S[i] = fmaf(s_w[tt][i], S[i], s_k[tt][i] * vj);
-                }
-                acc = fmaf(s_bonus[tt], vj, acc);
-            } else {
-#pragma unroll
-                for (int i = 0; i < DK; ++i) {
-                    S[i] = fmaf(lam, S[i], s_k[tt][i] * vj);
-                    acc = fmaf(s_r[tt][i], S[i], acc);
+                for (int i = 0; i < DK; i += 4) {
+                    const float4 kk = k4[i >> 2];
+                    const float4 ww = MODE == 0 ? w4[i >> 2] : make_float4(lam, lam, lam, lam);
+                    S[i] = fmaf(ww.x, S[i], kk.x * vj);
+                    S[i + 1] = fmaf(ww.y, S[i + 1], kk.y * vj);
+                    S[i + 2] = fmaf(ww.z, S[i + 2], kk.z * vj);
+                    S[i + 3] = fmaf(ww.w, S[i + 3], kk.w * vj);
                 }
             }
+            continue;
+        }
+        for (int tt = 0; tt < nt; ++tt) {
+            const float vj = s_v[tt][threadIdx.x];
+            const float4* r4 = reinterpret_cast<const float4*>(s_r[tt]);
+            const float4* k4 = reinterpret_cast<const float4*>(s_k[tt]);
+            const float4* w4 = reinterpret_cast<const float4*>(s_w[tt]);
+            float acc4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (MODE == 0) {
+#pragma unroll
+                for (int i = 0; i < DK; i += 4) {
+                    const float4 rr = r4[i >> 2], kk = k4[i >> 2], ww = w4[i >> 2];
+                    acc4[0] = fmaf(rr.x, S[i], acc4[0]);
+                    S[i] = fmaf(ww.x, S[i], kk.x * vj);
+                    acc4[1] = fmaf(rr.y, S[i + 1], acc4[1]);
+                    S[i + 1] = fmaf(ww.y, S[i + 1], kk.y * vj);
+                    acc4[2] = fmaf(rr.z, S[i + 2], acc4[2]);
+                    S[i + 2] = fmaf(ww.z, S[i + 2], kk.z * vj);
+                    acc4[3] = fmaf(rr.w, S[i + 3], acc4[3]);
+                    S[i + 3] = fmaf(ww.w, S[i + 3], kk.w * vj);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < DK; i += 4) {
+                    const float4 rr = r4[i >> 2], kk = k4[i >> 2];
+                    S[i] = fmaf(lam, S[i], kk.x * vj);
+                    acc4[0] = fmaf(rr.x, S[i], acc4[0]);
+                    S[i + 1] = fmaf(lam, S[i + 1], kk.y * vj);
+                    acc4[1] = fmaf(rr.y, S[i + 1], acc4[1]);
+                    S[i + 2] = fmaf(lam, S[i + 2], kk.z * vj);
+                    acc4[2] = fmaf(rr.z, S[i + 2], acc4[2]);
+                    S[i + 3] = fmaf(lam, S[i + 3], kk.w * vj);
+                    acc4[3] = fmaf(rr.w, S[i + 3], acc4[3]);
+                }
+            }
+            float acc = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
+            if (MODE == 0) acc = fmaf(s_bonus[tt], vj, acc);
             if (live) o[(size_t)(first + base + tt) * ((size_t)heads * dv) + (size_t)hd * dv + j] = acc;
         }
     }
-    if (live) {
+    if (live && write_state) {
 #pragma unroll
         for (int i = 0; i < DK; ++i) if (i < dk) st[i] = S[i];
     }
+    if (decay_out && blockIdx.z == 0) {
+        float all = 1.f;
+        if (MODE == 1) for (int t = 0; t < len; ++t) all *= lam;
+#pragma unroll
+        for (int m = 0; m < kOwn; ++m) {
+            const int i = threadIdx.x + m * kColThreads;
+            if (i < dk) decay_out[((size_t)e * heads + hd) * dk + i] = MODE == 0 ? expf(-dsum[m]) : all;
+        }
+    }
+}
+
+// Between the two passes over segments: seg_state [segments, heads, dv, dk] holds every segment's own contribution and
+// receives the state the segment starts from; seg_decay [segments, heads, dk] the product of each segment's decays.
+// Entry e owns segments entry_seg[e] .. entry_seg[e + 1] - 1; its request's state moves to the entry's end. A thread
+// owns one element of a head's matrix and fetches kChainAhead segments' numbers at a time, so that the walk waits for
+// memory once a group and not once a segment.
+constexpr int kChainThreads = 256, kChainAhead = 8;
+
+__global__ void __launch_bounds__(kChainThreads)
+matrix_state_chain_kernel(float* __restrict__ seg_state, const float* __restrict__ seg_decay, float* __restrict__ state,
+                          long long state_stride, const int* __restrict__ entry_seg, const int* __restrict__ start_pos,
+                          const int* __restrict__ slot_ids, int heads, int dk, int dv) {
+    qi::pdl_wait();
+    const int hd = blockIdx.x, e = blockIdx.y;
+    const int elems = dk * dv;
+    const int el = blockIdx.z * kChainThreads + threadIdx.x;
+    if (el >= elems) return;
+    const int s0 = entry_seg[e], s1 = entry_seg[e + 1];
+    float* st = state + (size_t)slot_ids[e] * state_stride + (size_t)hd * elems + el;
+    float S = start_pos[e] > 0 ? *st : 0.f;
+    const size_t seg_stride = (size_t)heads * elems, dec_stride = (size_t)heads * dk;
+    float* row = seg_state + ((size_t)s0 * heads + hd) * elems + el;
+    const float* dec = seg_decay + ((size_t)s0 * heads + hd) * dk + el % dk;
+    for (int s = s0; s < s1; s += kChainAhead) {
+        float own[kChainAhead], d[kChainAhead];
+#pragma unroll
+        for (int a = 0; a < kChainAhead; ++a) {
+            const bool in = s + a < s1;
+            own[a] = in ? row[a * seg_stride] : 0.f;
+            d[a] = in ? dec[a * dec_stride] : 1.f;
+        }
+#pragma unroll
+        for (int a = 0; a < kChainAhead; ++a) {
+            if (s + a < s1) {
+                row[a * seg_stride] = S;
+                S = fmaf(d[a], S, own[a]);
+            }
+        }
+        row += kChainAhead * seg_stride;
+        dec += kChainAhead * dec_stride;
+    }
+    *st = S;
 }
 
 // out = sa * a + sb * b, 32-bit, for the next norm's fused addition.
@@ -245,11 +434,17 @@ extern "C" int qi_token_shift(const void* h, int dtype, const float* mu, float* 
                               int channels, int n_mix, cudaStream_t stream) {
     QI_REQUIRE(n_tokens >= 0 && channels > 0 && n_mix > 0 && state_stride >= channels, "token_shift: bad sizes");
     if (n_tokens == 0) return 0;
-    const size_t total = (size_t)n_tokens * channels;
-    QI_REQUIRE((total + 255) / 256 <= 0x7fffffffull, "token_shift: grid too large");
     QI_DISPATCH_DTYPE(dtype, T, {
-        qi::launch(token_shift_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const T*)h, mu, state,
-                   state_stride, (T*)out, token_req, q_start, start_pos, slot_ids, n_tokens, channels, n_mix);
+        constexpr int kVec = 16 / (int)sizeof(T);
+        const bool wide = channels % kVec == 0 && (((uintptr_t)h | (uintptr_t)out) & 15) == 0;
+        const size_t total = (size_t)n_tokens * (wide ? channels / kVec : channels);
+        QI_REQUIRE((total + 255) / 256 <= 0x7fffffffull, "token_shift: grid too large");
+        if (wide)
+            qi::launch(token_shift_kernel<T, kVec>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const T*)h, mu, state,
+                       state_stride, (T*)out, token_req, q_start, start_pos, slot_ids, n_tokens, channels, n_mix);
+        else
+            qi::launch(token_shift_kernel<T, 1>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const T*)h, mu, state,
+                       state_stride, (T*)out, token_req, q_start, start_pos, slot_ids, n_tokens, channels, n_mix);
     });
     return qi::check_launch("token_shift");
 }
@@ -258,23 +453,27 @@ extern "C" int qi_matrix_state_scan_supported(int dk) { return dk > 0 && dk <= 2
 
 // mode 0: r, k, lw [n, >= heads dk], v [n, >= heads dv] in `dtype` (each with its own row stride); w0, u float32
 // [heads dk]; lambda unused. mode 1: r (the queries), k, v the same; lambda float32 [heads]; lw, w0, u unused.
-// state float32 [heads, dv, dk] a slot, `state_stride` floats apart; o float32 [n, heads dv].
+// state float32 [heads, dv, dk] a slot, `state_stride` floats apart; o float32 [n, heads dv], or null: no outputs
+// (a segment's own contribution is all that is wanted). decay_out (or null): float32 [n_entries, heads, dk], receives
+// the product of each entry's decays per key channel. write_state 0: the state is read, not written.
 extern "C" int qi_matrix_state_scan(int mode, const void* r, long long ldr, const void* k, long long ldk, const void* v, long long ldv,
                                     const void* lw, long long ldw, int dtype, const float* w0, const float* u, const float* lambda,
-                                    float* state, long long state_stride, float* o, const int* q_start, const int* start_pos,
-                                    const int* slot_ids, int n_entries, int heads, int dk, int dv, cudaStream_t stream) {
+                                    float* state, long long state_stride, float* o, float* decay_out, int write_state,
+                                    const int* q_start, const int* start_pos, const int* slot_ids, int n_entries, int heads,
+                                    int dk, int dv, cudaStream_t stream) {
     QI_REQUIRE(mode == 0 || mode == 1, "matrix_state_scan: unknown mode %d", mode);
     QI_REQUIRE(n_entries >= 0 && heads > 0 && dv > 0 && qi_matrix_state_scan_supported(dk), "matrix_state_scan: bad sizes (keys of 1..256)");
     QI_REQUIRE(ldr >= (long long)heads * dk && ldk >= (long long)heads * dk && ldv >= (long long)heads * dv, "matrix_state_scan: the rows are too short");
     QI_REQUIRE(mode == 1 || (lw && w0 && u && ldw >= (long long)heads * dk), "matrix_state_scan: the decay's operands are missing");
     QI_REQUIRE(mode == 0 || lambda, "matrix_state_scan: the heads' decays are missing");
     QI_REQUIRE(state_stride >= (long long)heads * dk * dv, "matrix_state_scan: the slots of the state overlap");
+    QI_REQUIRE(o || write_state, "matrix_state_scan: neither outputs nor the state are wanted");
     QI_REQUIRE(n_entries <= 65535 && (dv + kColThreads - 1) / kColThreads <= 65535, "matrix_state_scan: grid too large");
     if (n_entries == 0) return 0;
     const dim3 grid(heads, n_entries, (dv + kColThreads - 1) / kColThreads), block(kColThreads);
 #define QI_MS(DKP, MODE)                                                                                                        \
     qi::launch(matrix_state_scan_kernel<T, DKP, MODE>, grid, block, 0, stream, (const T*)r, ldr, (const T*)k, ldk, (const T*)v, ldv, \
-               (const T*)lw, ldw, w0, u, lambda, state, state_stride, o, q_start, start_pos, slot_ids, heads, dk, dv)
+               (const T*)lw, ldw, w0, u, lambda, state, state_stride, o, decay_out, write_state, q_start, start_pos, slot_ids, heads, dk, dv)
 #define QI_MS_DK(MODE)                              \
     if (dk <= 16) QI_MS(16, MODE);                  \
     else if (dk <= 32) QI_MS(32, MODE);             \
@@ -287,6 +486,20 @@ extern "C" int qi_matrix_state_scan(int mode, const void* r, long long ldr, cons
 #undef QI_MS_DK
 #undef QI_MS
     return qi::check_launch("matrix_state_scan");
+}
+
+// seg_state float32 [segments, heads, dv, dk]; seg_decay float32 [segments, heads, dk]; state float32 [heads, dv, dk] a
+// slot; entry_seg [n_entries + 1].
+extern "C" int qi_matrix_state_chain(float* seg_state, const float* seg_decay, float* state, long long state_stride,
+                                     const int* entry_seg, const int* start_pos, const int* slot_ids, int n_entries, int heads,
+                                     int dk, int dv, cudaStream_t stream) {
+    QI_REQUIRE(n_entries >= 0 && heads > 0 && dk > 0 && dv > 0, "matrix_state_chain: bad sizes");
+    QI_REQUIRE(state_stride >= (long long)heads * dk * dv, "matrix_state_chain: the slots of the state overlap");
+    QI_REQUIRE(n_entries <= 65535, "matrix_state_chain: grid too large");
+    if (n_entries == 0) return 0;
+    qi::launch(matrix_state_chain_kernel, dim3(heads, n_entries, (dk * dv + kChainThreads - 1) / kChainThreads), dim3(kChainThreads), 0, stream, seg_state,
+               seg_decay, state, state_stride, entry_seg, start_pos, slot_ids, heads, dk, dv);
+    return qi::check_launch("matrix_state_chain");
 }
 
 // a, b [n] in `dtype`; out float32 [n].

@@ -485,6 +485,48 @@ gated_group_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z
     }
 }
 
+// The same for narrow groups (up to kNarrowGroup coordinates): a warp a group, eight groups a block, no barrier.
+constexpr int kNarrowGroup = 256;
+
+template <typename TZ, typename TO>
+__global__ void __launch_bounds__(256)
+gated_narrow_group_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, long long ldz, const float* __restrict__ gain,
+                                  float eps, TO* __restrict__ out, long long n_groups, int width, int groups, int mode, float out_scale) {
+    qi::pdl_wait();
+    const long long g = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (g >= n_groups) return;
+    const int lane = threadIdx.x & 31;
+    const size_t t = (size_t)(g / groups);
+    const int grp = (int)(g % groups);
+    const int gw = width / groups;
+    const float* yr = y + t * width + (size_t)grp * gw;
+    const TZ* zr = z + t * ldz + (size_t)grp * gw;
+    constexpr int kOwn = kNarrowGroup / 32;
+    float v[kOwn], zz[kOwn];
+    float ss = 0.f;
+#pragma unroll
+    for (int m = 0; m < kOwn; ++m) {
+        const int i = lane + 32 * m;
+        v[m] = i < gw ? yr[i] : 0.f;
+        zz[m] = i < gw ? qi::to_f32<TZ>(zr[i]) : 0.f;
+        if (mode == 0) v[m] *= zz[m] / (1.0f + expf(-zz[m]));
+        ss = fmaf(v[m], v[m], ss);
+    }
+    const float inv = 1.0f / sqrtf(qi::warp_sum(ss) / (float)gw + eps);
+#pragma unroll
+    for (int m = 0; m < kOwn; ++m) {
+        const int i = lane + 32 * m;
+        if (i < gw) {
+            const float sg = 1.0f / (1.0f + expf(-zz[m]));
+            float r = v[m] * inv * gain[(size_t)grp * gw + i];
+            if (mode == 1) r *= zz[m] * sg;
+            else if (mode == 2) r *= sg;
+            else if (mode == 3) r *= zz[m];
+            out[t * width + (size_t)grp * gw + i] = qi::from_f32<TO>(r * out_scale);
+        }
+    }
+}
+
 }  // namespace
 
 // xbc [n, >= heads P + 2 groups N] in `dtype` (x | B | C, `ldx` elements a row); raw_dt [n, >= heads] in `dtype`, column h
@@ -594,10 +636,16 @@ extern "C" int qi_group_rmsnorm_gate(const float* y, const void* z, int z_dtype,
     QI_REQUIRE(ldz >= width && groups <= 65535, "gated_group_rmsnorm: bad layout");
     QI_REQUIRE(mode >= 0 && mode <= 3, "gated_group_rmsnorm: unknown mode %d", mode);
     if (n == 0) return 0;
+    const long long n_groups = (long long)n * groups;
+    const bool narrow = width / groups <= kNarrowGroup && groups > 1 && (n_groups + 7) / 8 <= 0x7fffffffll;
     QI_DISPATCH_DTYPE(z_dtype, TZ, {
         QI_DISPATCH_DTYPE(out_dtype, TO, {
-            qi::launch(gated_group_rmsnorm_kernel<TZ, TO>, dim3(n, groups), dim3(256), 0, stream, y, (const TZ*)z, ldz, gain, eps,
-                       (TO*)out, width, groups, mode, out_scale);
+            if (narrow)
+                qi::launch(gated_narrow_group_rmsnorm_kernel<TZ, TO>, dim3((unsigned)((n_groups + 7) / 8)), dim3(256), 0, stream, y,
+                           (const TZ*)z, ldz, gain, eps, (TO*)out, n_groups, width, groups, mode, out_scale);
+            else
+                qi::launch(gated_group_rmsnorm_kernel<TZ, TO>, dim3(n, groups), dim3(256), 0, stream, y, (const TZ*)z, ldz, gain, eps,
+                           (TO*)out, width, groups, mode, out_scale);
         });
     });
     return qi::check_launch("gated_group_rmsnorm");

@@ -411,7 +411,7 @@ def attention_prefill_ranges(n_ctas: int, max_kv_len: int) -> int:
 def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos, tile_req, tile_q0,
                       nq, nkv, d, scale: float, window: int, status, use_tma: bool | None = None,
                       impl: str | None = None, max_kv_len: int = 0, key_ranges: int | None = None, chunk: int = 0,
-                      gate=None) -> None:
+                      gate=None, softcap: float = 0.0, out_scale: float = 1.0) -> None:
     """Causal paged GQA flash attention (bfloat16, head size 64 or 128) for spans of any
     length. `tile_req[i]`, `tile_q0[i]`: request index and first flat token of the i-th
     block of up to QUERY_TILE query rows.
@@ -423,8 +423,9 @@ def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos,
     the last two. `max_kv_len` (the longest context of the step) lets the tcgen05 kernel cut long
     contexts into key ranges over more CTAs (`key_ranges` forces a number). The tcgen05 kernel alone takes
     `chunk` (a query sees only the keys of its own chunk of that many positions, counted from the sequence's
-    start) and `gate` (bfloat16 [n, nq d], rows a multiple of 8 elements apart and 16-byte aligned: the output is
-    multiplied with its sigmoid)."""
+    start), `gate` (bfloat16 [n, nq d], rows a multiple of 8 elements apart and 16-byte aligned: the output is
+    multiplied with its sigmoid), `softcap` c > 0 (a score s becomes c tanh(s / c)) and `out_scale` (a factor on the
+    result)."""
     if impl is None and use_tma is not None:
         impl = "tma" if use_tma else "cpasync"
     _req(q, "q", torch.bfloat16, 2)
@@ -461,10 +462,10 @@ def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos,
               _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
             k_pages.shape[2], k_pages.shape[0], _ptr(q_start), _ptr(start_pos), _ptr(tile_req), _ptr(tile_q0),
             tile_req.numel(), q.shape[0], nq, nkv, d, C.c_float(scale), int(window or 0), int(chunk or 0), _ptr(gate),
-            C.c_longlong(ldg), ranges, _ptr(ws), _ptr(status), _stream())
+            C.c_longlong(ldg), ranges, _ptr(ws), _ptr(status), C.c_float(softcap or 0.0), C.c_float(out_scale), _stream())
         return
-    if chunk or gate is not None:
-        raise KernelError(f"attention_prefill: the {impl!r} kernel takes neither a chunk bound nor a gate")
+    if chunk or gate is not None or softcap or out_scale != 1.0:
+        raise KernelError(f"attention_prefill: the {impl!r} kernel takes neither a chunk bound, a gate, a soft cap nor an output factor")
     if impl not in ("tma", "cpasync"):
         raise KernelError(f"attention_prefill: unknown kernel {impl!r}")
     if impl == "tma":
@@ -1258,13 +1259,15 @@ def token_shift(h, mu, state, out, token_req, q_start, start_pos, slot_ids) -> N
 
 
 def matrix_state_scan(mode: str, r, k, v, state, o, q_start, start_pos, slot_ids, heads: int, dk: int, dv: int, *, log_decay=None,
-                      decay_bias=None, bonus=None, head_decay=None) -> None:
+                      decay_bias=None, bonus=None, head_decay=None, decay_out=None, write_state: bool = True) -> None:
     """A recurrence over a matrix state S [dk, dv] a head that decays and receives k_t v_t^T with every token.
     mode "channel_decay": o_t = S_(t-1)^T r_t + (sum_i r_i bonus_i k_i) v_t, then S_t = diag(w_t) S_(t-1) + k_t v_t^T with
     w_t = exp(-exp(log_decay_t + decay_bias)) per head and key channel. mode "head_decay": r, k, v pass silu first,
     S_t = head_decay S_(t-1) + k_t v_t^T, o_t = S_t^T r_t. r, k, log_decay [n, heads dk], v [n, heads dv] (blocks of
     columns of wider rows are fine); decay_bias, bonus float32 [heads dk]; head_decay float32 [heads]; state float32
-    [slots, heads, dv, dk]; o float32 [n, heads dv]."""
+    [slots, heads, dv, dk]; o float32 [n, heads dv], or None: the state moves on and nothing else is written. decay_out
+    (or None): float32 [entries, heads, dk], receives the product of each entry's decays per key channel. write_state
+    False: the state is only read. The last three serve long entries cut into segments (`matrix_state_chain`)."""
     if mode not in ("channel_decay", "head_decay"):
         raise KernelError(f"matrix_state_scan: unknown mode {mode!r}")
     for t, name in ((r, "r"), (k, "k"), (v, "v")):
@@ -1284,15 +1287,42 @@ def matrix_state_scan(mode: str, r, k, v, state, o, q_start, start_pos, slot_ids
         if head_decay.numel() != heads:
             raise KernelError("matrix_state_scan: one decay a head")
     _req_state(state, "state", torch.float32)
-    _req(o, "o", torch.float32, 2)
-    if tuple(state.shape[1:]) != (heads, dv, dk) or tuple(o.shape) != (n, heads * dv):
-        raise KernelError(f"matrix_state_scan: state {tuple(state.shape)} / o {tuple(o.shape)} do not fit")
+    if o is not None:
+        _req(o, "o", torch.float32, 2)
+    elif not write_state:
+        raise KernelError("matrix_state_scan: neither outputs nor the state are wanted")
+    if tuple(state.shape[1:]) != (heads, dv, dk) or (o is not None and tuple(o.shape) != (n, heads * dv)):
+        raise KernelError(f"matrix_state_scan: state {tuple(state.shape)} / o do not fit")
     for t, name in ((q_start, "q_start"), (start_pos, "start_pos"), (slot_ids, "slot_ids")):
         _req(t, name, torch.int32, 1)
+    if decay_out is not None:
+        _req(decay_out, "decay_out", torch.float32, 3)
+        if tuple(decay_out.shape) != (start_pos.numel(), heads, dk):
+            raise KernelError("matrix_state_scan: decay_out must be [entries, heads, dk]")
     _call("scan", "matrix_state_scan", library().qi_matrix_state_scan, 0 if channel else 1, _ptr(r), C.c_longlong(r.stride(0)), _ptr(k),
           C.c_longlong(k.stride(0)), _ptr(v), C.c_longlong(v.stride(0)), _ptr(log_decay), C.c_longlong(log_decay.stride(0) if channel else 0),
           _code(r), _ptr(decay_bias), _ptr(bonus), _ptr(head_decay), _ptr(state), C.c_longlong(state.stride(0)), _ptr(o),
-          _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), start_pos.numel(), heads, dk, dv, _stream())
+          _ptr(decay_out), int(bool(write_state)), _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), start_pos.numel(), heads, dk, dv,
+          _stream())
+
+
+def matrix_state_chain(seg_state, seg_decay, state, entry_seg, start_pos, slot_ids) -> None:
+    """Between the two passes of `matrix_state_scan` over a long entry's segments: seg_state [segments, heads, dv, dk]
+    holds every segment's own contribution and receives the state each segment starts from; seg_decay [segments, heads, dk]
+    the product of each segment's decays; the requests' states (state [slots, heads, dv, dk]) move to their entries'
+    ends. entry_seg [entries + 1]: the first segment of every entry."""
+    _req(seg_state, "seg_state", torch.float32, 4)
+    _req(seg_decay, "seg_decay", torch.float32, 3)
+    _req_state(state, "state", torch.float32)
+    segs, heads, dv, dk = seg_state.shape
+    if tuple(state.shape[1:]) != (heads, dv, dk) or tuple(seg_decay.shape) != (segs, heads, dk):
+        raise KernelError("matrix_state_chain: shapes do not agree")
+    for t, name in ((entry_seg, "entry_seg"), (start_pos, "start_pos"), (slot_ids, "slot_ids")):
+        _req(t, name, torch.int32, 1)
+    if entry_seg.numel() != start_pos.numel() + 1:
+        raise KernelError("matrix_state_chain: the segment list does not fit the entries")
+    _call("scan", "matrix_state_chain", library().qi_matrix_state_chain, _ptr(seg_state), _ptr(seg_decay), _ptr(state),
+          C.c_longlong(state.stride(0)), _ptr(entry_seg), _ptr(start_pos), _ptr(slot_ids), start_pos.numel(), heads, dk, dv, _stream())
 
 
 def scaled_sum(a, b, sa: float, sb: float, out) -> None:
@@ -1428,10 +1458,8 @@ def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv
     cores, tiles found on the device from the step's arrays) or "generic" (32-bit arithmetic, any sizes). A step
     with prompt portions whose keys and values are both of size 128 goes to "tcgen05": the portions' query tiles
     to the tcgen05 flash kernel (chunk bound and gate included), the single tokens in front of them to "mma".
-    `softcap` c > 0 (a score s becomes c tanh(s / c)) and `out_scale` (a factor on the result) are known to "mma" and
-    "generic"."""
-    plain = not softcap and out_scale == 1.0
-    if impl is None and plain and q.dtype == torch.bfloat16 and d == dv and not batch.all_decode and batch.tile_req.numel() and (
+    `softcap` c > 0 (a score s becomes c tanh(s / c)) and `out_scale` (a factor on the result) are known to all three."""
+    if impl is None and q.dtype == torch.bfloat16 and d == dv and not batch.all_decode and batch.tile_req.numel() and (
             gate is None or (gate.stride(0) % 8 == 0 and gate.data_ptr() % 16 == 0)) and attention_prefill_tcgen05_supported(
             nq, nkv, d, k_pages.shape[2], block_table.shape[1]):
         impl = "tcgen05"
@@ -1439,12 +1467,11 @@ def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv
         lead = batch.n_lead_decode
         if lead:
             gated_attention(q[:lead], out[:lead], k_pages, v_pages, block_table[:lead], _LeadRows(batch, lead), nq, nkv, d, dv,
-                            scale, window, chunk, gate[:lead] if gate is not None else None, status, impl="mma")
-        if not plain:
-            raise KernelError("gated_attention: the tcgen05 kernel knows neither a soft cap nor an output factor")
+                            scale, window, chunk, gate[:lead] if gate is not None else None, status, impl="mma", softcap=softcap,
+                            out_scale=out_scale)
         return attention_prefill(q, out, k_pages, v_pages, block_table, batch.q_start, batch.start_pos, batch.tile_req,
                                  batch.tile_q0, nq, nkv, d, scale, window, status, impl="tcgen05", max_kv_len=batch.max_kv_len,
-                                 key_ranges=1 if chunk else None, chunk=chunk, gate=gate)
+                                 key_ranges=1 if chunk else None, chunk=chunk, gate=gate, softcap=softcap, out_scale=out_scale)
     if impl is None:
         impl = "mma" if q.dtype == torch.bfloat16 and gated_attention_mma_supported(nq, nkv, d, dv) and (
             gate is None or gate.stride(0) % 2 == 0) else "generic"

@@ -13,6 +13,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
+from . import segments
 from ..cache.needs import StateNeed
 from ..errors import ConfigError
 from ..weights.loader import TensorNeed
@@ -58,8 +59,8 @@ class LightningAttention(Part):
         qk, inner = self.qk, self.inner
         S = cache.state.unflatten(1, (s.heads, s.value_dim, s.head_dim))
         o = torch.empty((n, inner), dtype=torch.float32, device=x.device)
-        kernels.matrix_state_scan("head_decay", proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + inner], S, o, batch.q_start,
-                                  batch.start_pos, batch.slot_ids, s.heads, s.head_dim, s.value_dim, head_decay=self.decays)
+        segments.matrix_state_scan("head_decay", proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + inner], S, o, batch,
+                                   s.heads, s.head_dim, s.value_dim, head_decay=self.decays)
         y = torch.empty((n, inner), dtype=x.dtype, device=x.device)
         kernels.gated_group_rmsnorm(o, proj[:, 2 * qk + inner:], self.gain, s.norm_eps, y, 1, gate="sigmoid", out_scale=s.out_scale)
         return self.o(y, keep_partials=True)

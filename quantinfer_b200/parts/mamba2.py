@@ -22,6 +22,7 @@ from .. import kernels
 from ..cache.needs import StateNeed
 from ..errors import ConfigError
 from ..weights.loader import TensorNeed
+from . import segments
 from .base import Part, register_part
 from .linear import Linear
 
@@ -65,31 +66,11 @@ class Mamba2(Part):
         s = self.spec
         return StateNeed((self.conv_floats + s.heads * s.head_dim * s.state,), torch.float32)
 
-    SEGMENT = 64          # tokens a segment of a long entry
-    SEGMENT_FROM = 192    # entries shorter than this run in one piece
+    SEGMENT, SEGMENT_FROM = segments.SEGMENT, segments.SEGMENT_FROM
 
     def _segments(self, batch):
-        """The step's entries cut into segments, when one of them is long and the step runs once (a step that may be
-        replayed from a CUDA graph holds single tokens and has no host-side lists): (first rows of the segments, first
-        segments of the entries, zeros, ones, scratch rows, most segments an entry) on the device, shared by the
-        step's layers through `batch.extra`."""
-        if batch.extra.get("graph") or batch.max_q_len < self.SEGMENT_FROM:
-            return None
-        if "ssm_segments" not in batch.extra:
-            starts, entry_seg, longest = [], [0], 0
-            q = batch.h_q_start
-            for a, b in zip(q[:-1], q[1:]):
-                cuts = list(range(a, b, self.SEGMENT)) if b - a >= self.SEGMENT_FROM else [a]
-                starts += cuts
-                entry_seg.append(len(starts))
-                longest = max(longest, len(cuts))
-            n_seg = len(starts)
-            host = torch.tensor(starts + [q[-1]] + entry_seg + [0] * n_seg + [1] * n_seg + list(range(n_seg)), dtype=torch.int32)
-            dev = host.to(batch.q_start.device, non_blocking=True)
-            o = [n_seg + 1, n_seg + 1 + len(entry_seg)]
-            batch.extra["ssm_segments"] = (dev[:o[0]], dev[o[0]:o[1]], dev[o[1]:o[1] + n_seg], dev[o[1] + n_seg:o[1] + 2 * n_seg],
-                                           dev[o[1] + 2 * n_seg:], longest)
-        return batch.extra["ssm_segments"]
+        """The step's entries cut into segments when one of them is long (`segments.entry_segments`)."""
+        return segments.entry_segments(batch, self.SEGMENT, self.SEGMENT_FROM)
 
     def forward(self, x, batch, cache):
         s = self.spec

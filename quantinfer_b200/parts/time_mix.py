@@ -15,6 +15,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
+from . import segments
 from ..cache.needs import StateNeed
 from ..errors import ConfigError, WeightError
 from ..weights.loader import TensorNeed
@@ -76,8 +77,8 @@ class TimeMix(Part):
         kernels.activation(low, low, "tanh")
         log_decay = self.w2(low)
         o = torch.empty((n, self.inner), dtype=torch.float32, device=x.device)
-        kernels.matrix_state_scan("channel_decay", r, k, v, S, o, batch.q_start, batch.start_pos, batch.slot_ids, s.heads, s.head_dim,
-                                  s.head_dim, log_decay=log_decay, decay_bias=self.w0, bonus=self.u)
+        segments.matrix_state_scan("channel_decay", r, k, v, S, o, batch, s.heads, s.head_dim, s.head_dim, log_decay=log_decay,
+                                   decay_bias=self.w0, bonus=self.u)
         y = torch.empty((n, self.inner), dtype=x.dtype, device=x.device)
         kernels.gated_group_rmsnorm(o, g, self.gain, s.norm_eps, y, s.heads, gate="silu")
         return self.o(y, keep_partials=True)

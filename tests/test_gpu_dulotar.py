@@ -322,6 +322,58 @@ def test_capped_scores_in_both_attention_kernels(impl, dtype, H, G, d, dv, chunk
     assert float(err.max()) < (1e-4 if dtype == torch.float32 else 0.04), (float(err.max()), np.unravel_index(int(err.argmax()), err.shape))
 
 
+@pytest.mark.parametrize("H, G, chunk, cap, page", [(4, 2, 100, 3.0, 16), (2, 1, 0, 8.0, 64), (3, 3, 64, 0.0, 8)])
+def test_capped_scores_in_the_tcgen05_attention_kernel(H, G, chunk, cap, page):
+    """Heads of 128 / 128 go to the tcgen05 kernel when a step has prompt portions: scores several times the cap, a chunk
+    bound that is no multiple of a key tile, a decode token in front of two portions (one of more than a query tile),
+    pages in shuffled order, a factor on the result."""
+    from types import SimpleNamespace
+    from quantinfer_b200 import kernels as k
+
+    d = dv = 128
+    torch.manual_seed(H + chunk)
+    lens, starts = [1, 150, 70], [90, 0, 45]
+    B, n = len(lens), sum(lens)
+    ctx = [s + l for s, l in zip(starts, lens)]
+    blocks = max(-(-c // page) for c in ctx)
+    table = torch.randperm(B * blocks + 3)[:B * blocks].view(B, blocks).to(torch.int32)
+    kp = torch.zeros(B * blocks + 3, G, page, d)
+    vp = torch.zeros(B * blocks + 3, G, page, dv)
+    keys = [(torch.randn(c, G, d) * 1.0).to(torch.bfloat16).float() for c in ctx]
+    vals = [torch.randn(c, G, dv).to(torch.bfloat16).float() for c in ctx]
+    q = (torch.randn(n, H, d) * 1.0).to(torch.bfloat16).float()
+    scale, out_scale = 0.5, 0.7
+    ref = torch.zeros(n, H, dv, dtype=torch.float64)
+    a, capped = 0, 0
+    for e in range(B):
+        for j in range(ctx[e]):
+            kp[table[e, j // page], :, j % page] = keys[e][j]
+            vp[table[e, j // page], :, j % page] = vals[e][j]
+        for t in range(lens[e]):
+            pos = starts[e] + t
+            lo = pos // chunk * chunk if chunk else 0
+            for hq in range(H):
+                g = hq // (H // G)
+                s = (keys[e][lo:pos + 1, g].double() @ q[a + t, hq].double()) * scale
+                if cap:
+                    capped += int((s.abs() > 2 * cap).sum())
+                    s = cap * torch.tanh(s / cap)
+                ref[a + t, hq] = out_scale * (torch.softmax(s, 0) @ vals[e][lo:pos + 1, g].double())
+        a += lens[e]
+    assert not cap or capped > 100          # the premise: the cap bites
+    q0, sp, _, token_req = _entries(lens, starts)
+    batch = SimpleNamespace(q_start=q0, start_pos=sp, n_requests=B, token_req=token_req, all_decode=False, n_lead_decode=1,
+                            positions=_i([s0 + i for s0, ln in zip(starts, lens) for i in range(ln)]), max_kv_len=max(ctx),
+                            tile_req=_i([1, 1, 2]), tile_q0=_i([1, 129, 151]))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((n, H * dv), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.gated_attention(_d(q.view(n, H * d).to(torch.bfloat16)), out, _d(kp.to(torch.bfloat16)), _d(vp.to(torch.bfloat16)), _d(table), batch, H, G,
+                      d, dv, scale, 0, chunk, None, status, softcap=cap, out_scale=out_scale, impl="tcgen05")
+    assert int(status.item()) == 0
+    err = (out.cpu().double().view(n, H, dv) - ref).abs()
+    assert float(err.max()) < 0.04, (float(err.max()), np.unravel_index(int(err.argmax()), err.shape))
+
+
 # ---------------------------------------------------------------- one mixer alone, in an engine of one layer
 
 
@@ -456,6 +508,32 @@ def test_the_branches_far_into_a_sequence(tmp_path, dtype):
     got = _run(eng, x, [1000, 37] + [1] * 63)
     err = float((got.double() - ref).abs().max())
     assert err < (2e-4 if dtype == "float32" else 0.08), err
+
+
+@pytest.mark.parametrize("cuts", [[500], [250, 250], [193, 7, 300], [40, 460]])
+@pytest.mark.parametrize("kind, sizes", [("wkv", (3, 6)), ("wkv", (1, 72)), ("wkv", (2, 130)), ("parallel", (3, 5, 7)), ("parallel", (1, 80, 70)),
+                                         ("parallel", (2, 16, 130)), ("mingru", (30,))])
+def test_long_entries_run_as_segments_side_by_side(tmp_path, cuts, kind, sizes):
+    """Entries of 192 tokens and more are cut into segments of 64 that run at once and are chained through their states;
+    a portion's last segment is short, and the request's state must come out as if the tokens had run in a row (the
+    single tokens behind the portions read it). Keys of 5 to 130 numbers: fewer than a block's threads, and several a
+    thread; more value columns than one block takes."""
+    if kind == "wkv":
+        entry = wkv(*sizes, rank=4)
+    elif kind == "parallel":
+        entry = parallel(left(2, 1, 8, 8, rot_dims=4, chunk=48, conv=2), right(*sizes, (0.97, 0.8, 0.995)[:sizes[0]]), 0.1, 1.0)
+    else:
+        entry = mingru(*sizes)
+    eng, cfg, w = _one_layer(tmp_path, entry, 24, "float32", seed=21, eps=2e-6, max_tokens=1024)
+    torch.manual_seed(15)
+    x = torch.randn(sum(cuts) + 30, 24)
+    _run(eng, torch.randn(200, 24) * 3.0, [200], rid="earlier")       # the slot's earlier owner leaves its state behind
+    m = cfg["layers"][0]["mixer"]
+    ref = {"wkv": lambda: plain.wkv(x.double(), m, w, "l0.mix.", 2e-6), "parallel": lambda: plain.parallel_mixer(x.double(), m, w, "l0.mix.", 2e-6),
+           "mingru": lambda: plain.mingru(x.double(), m, w, "l0.mix.")}[kind]()
+    got = _run(eng, x, cuts + [1] * 30)
+    err = (got.double() - ref).abs().max(dim=1).values
+    assert float(err.max()) < 2e-4 * max(1.0, float(ref.abs().max())), (int(err.argmax()), float(err.max()))
 
 
 @pytest.mark.parametrize("kind", ["mingru", "wkv", "parallel"])
