@@ -172,7 +172,7 @@ token_shift_kernel(const T* __restrict__ h, const float* __restrict__ mu, float*
 constexpr int kColThreads = 64;
 
 template <typename T, int DK, int MODE>
-__global__ void __launch_bounds__(kColThreads)
+__global__ void __launch_bounds__(kColThreads, (DK <= 64 ? 8 : 1))
 matrix_state_scan_kernel(const T* __restrict__ r, long long ldr, const T* __restrict__ k, long long ldk, const T* __restrict__ v,
                          long long ldv, const T* __restrict__ lw, long long ldw, const float* __restrict__ w0,
                          const float* __restrict__ u, const float* __restrict__ lambda, float* __restrict__ state,
@@ -194,9 +194,20 @@ matrix_state_scan_kernel(const T* __restrict__ r, long long ldr, const T* __rest
     float S[DK];
 #pragma unroll
     for (int i = 0; i < DK; ++i) S[i] = 0.f;
+    // a column is dk numbers in a row: 16 bytes a load where the column starts on such a boundary
+    const bool wide = dk % 4 == 0 && (reinterpret_cast<size_t>(st) & 15) == 0;
     if (live && start_pos[e] > 0) {
+        if (wide) {
 #pragma unroll
-        for (int i = 0; i < DK; ++i) if (i < dk) S[i] = st[i];
+            for (int i = 0; i < DK; i += 4)
+                if (i < dk) {
+                    const float4 x = *reinterpret_cast<const float4*>(st + i);
+                    S[i] = x.x, S[i + 1] = x.y, S[i + 2] = x.z, S[i + 3] = x.w;
+                }
+        } else {
+#pragma unroll
+            for (int i = 0; i < DK; ++i) if (i < dk) S[i] = st[i];
+        }
     }
     const float lam = MODE == 1 ? lambda[hd] : 0.f;
     float w0r[kOwn], dsum[kOwn];        // dsum: minus the logarithm of the product of this entry's decays
@@ -341,8 +352,14 @@ matrix_state_scan_kernel(const T* __restrict__ r, long long ldr, const T* __rest
         }
     }
     if (live && write_state) {
+        if (wide) {
 #pragma unroll
-        for (int i = 0; i < DK; ++i) if (i < dk) st[i] = S[i];
+            for (int i = 0; i < DK; i += 4)
+                if (i < dk) *reinterpret_cast<float4*>(st + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < DK; ++i) if (i < dk) st[i] = S[i];
+        }
     }
     if (decay_out && blockIdx.z == 0) {
         float all = 1.f;
@@ -398,12 +415,18 @@ matrix_state_chain_kernel(float* __restrict__ seg_state, const float* __restrict
     *st = S;
 }
 
-// out = sa * a + sb * b, 32-bit, for the next norm's fused addition.
-template <typename T>
-__global__ void scaled_sum_kernel(const T* __restrict__ a, const T* __restrict__ b, float sa, float sb, float* __restrict__ out, size_t n) {
+// out = sa * (a_0 + a_1 + ...) + sb * (b_0 + b_1 + ...), 32-bit, for the next norm's fused addition: a and b each come
+// whole or as the partial sums of a product whose contraction was split (ka, kb parts of n numbers, added in order).
+template <typename TA, typename TB>
+__global__ void scaled_sum_kernel(const TA* __restrict__ a, int ka, const TB* __restrict__ b, int kb, float sa, float sb,
+                                  float* __restrict__ out, size_t n) {
     qi::pdl_wait();
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x)
-        out[idx] = fmaf(sa, qi::to_f32<T>(a[idx]), sb * qi::to_f32<T>(b[idx]));
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+        float x = qi::to_f32<TA>(a[idx]), y = qi::to_f32<TB>(b[idx]);
+        for (int p = 1; p < ka; ++p) x += qi::to_f32<TA>(a[(size_t)p * n + idx]);
+        for (int p = 1; p < kb; ++p) y += qi::to_f32<TB>(b[(size_t)p * n + idx]);
+        out[idx] = fmaf(sa, x, sb * y);
+    }
 }
 
 }  // namespace
@@ -490,6 +513,27 @@ extern "C" int qi_matrix_state_scan(int mode, const void* r, long long ldr, cons
 
 // seg_state float32 [segments, heads, dv, dk]; seg_decay float32 [segments, heads, dk]; state float32 [heads, dv, dk] a
 // slot; entry_seg [n_entries + 1].
+// Blocks of the scan kernel (mode, key size, operand type) that one SM holds at a time, or 0 when it cannot be told:
+// whoever cuts long entries into segments sizes them so that the launch fills whole waves.
+extern "C" int qi_matrix_state_scan_blocks_per_sm(int mode, int dk, int dtype) {
+    if ((mode != 0 && mode != 1) || !qi_matrix_state_scan_supported(dk) || (dtype != qi::kF32 && dtype != qi::kBF16)) return 0;
+    int blocks = 0;
+#define QI_MS_OCC(DKP, MODE) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, matrix_state_scan_kernel<T, DKP, MODE>, kColThreads, 0)
+#define QI_MS_OCC_DK(MODE)                          \
+    if (dk <= 16) QI_MS_OCC(16, MODE);              \
+    else if (dk <= 32) QI_MS_OCC(32, MODE);         \
+    else if (dk <= 64) QI_MS_OCC(64, MODE);         \
+    else if (dk <= 128) QI_MS_OCC(128, MODE);       \
+    else QI_MS_OCC(256, MODE)
+    QI_DISPATCH_DTYPE(dtype, T, {
+        if (mode == 0) { QI_MS_OCC_DK(0); } else { QI_MS_OCC_DK(1); }
+    });
+#undef QI_MS_OCC_DK
+#undef QI_MS_OCC
+    if (cudaGetLastError() != cudaSuccess) return 0;
+    return blocks;
+}
+
 extern "C" int qi_matrix_state_chain(float* seg_state, const float* seg_decay, float* state, long long state_stride,
                                      const int* entry_seg, const int* start_pos, const int* slot_ids, int n_entries, int heads,
                                      int dk, int dv, cudaStream_t stream) {
@@ -502,14 +546,18 @@ extern "C" int qi_matrix_state_chain(float* seg_state, const float* seg_decay, f
     return qi::check_launch("matrix_state_chain");
 }
 
-// a, b [n] in `dtype`; out float32 [n].
-extern "C" int qi_scaled_sum(const void* a, const void* b, int dtype, float sa, float sb, float* out, long long n, cudaStream_t stream) {
-    QI_REQUIRE(n >= 0, "scaled_sum: bad size");
+// a [ka, n] in `dtype_a`, b [kb, n] in `dtype_b` (parts n numbers apart); out float32 [n].
+extern "C" int qi_scaled_sum(const void* a, int ka, int dtype_a, const void* b, int kb, int dtype_b, float sa, float sb, float* out,
+                             long long n, cudaStream_t stream) {
+    QI_REQUIRE(n >= 0 && ka >= 1 && kb >= 1, "scaled_sum: bad sizes");
     if (n == 0) return 0;
     size_t blocks = ((size_t)n + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
-    QI_DISPATCH_DTYPE(dtype, T, {
-        qi::launch(scaled_sum_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (const T*)a, (const T*)b, sa, sb, out, (size_t)n);
+    QI_DISPATCH_DTYPE(dtype_a, TA, {
+        QI_DISPATCH_DTYPE(dtype_b, TB, {
+            qi::launch(scaled_sum_kernel<TA, TB>, dim3((unsigned)blocks), dim3(256), 0, stream, (const TA*)a, ka, (const TB*)b, kb, sa, sb,
+                       out, (size_t)n);
+        });
     });
     return qi::check_launch("scaled_sum");
 }

@@ -1326,14 +1326,32 @@ def matrix_state_chain(seg_state, seg_decay, state, entry_seg, start_pos, slot_i
 
 
 def scaled_sum(a, b, sa: float, sb: float, out) -> None:
-    """out = sa * a + sb * b in 32-bit; a, b of one type and shape, out float32."""
+    """out = sa * a + sb * b in 32-bit; out float32 [n, h]. a and b are [n, h] each, or [parts, n, h]: the partial sums of
+    a product whose contraction was split, added here in their order. Their types may differ."""
     _req(a, "a")
-    _req(b, "b", a.dtype)
+    _req(b, "b")
     _req(out, "out", torch.float32)
-    if a.shape != b.shape or out.shape != a.shape:
-        raise KernelError("scaled_sum: shapes differ")
-    _call("other", "scaled_sum", library().qi_scaled_sum, _ptr(a), _ptr(b), _code(a), C.c_float(sa), C.c_float(sb), _ptr(out),
-          C.c_longlong(a.numel()), _stream())
+    for t in (a, b):
+        if t.dim() not in (out.dim(), out.dim() + 1) or tuple(t.shape[-out.dim():]) != tuple(out.shape) or not t.shape[0]:
+            raise KernelError("scaled_sum: shapes differ")
+    ka = a.shape[0] if a.dim() > out.dim() else 1
+    kb = b.shape[0] if b.dim() > out.dim() else 1
+    _call("other", "scaled_sum", library().qi_scaled_sum, _ptr(a), ka, _code(a), _ptr(b), kb, _code(b), C.c_float(sa), C.c_float(sb),
+          _ptr(out), C.c_longlong(out.numel()), _stream())
+
+
+MATRIX_STATE_COLUMNS = 64      # value columns a block of `matrix_state_scan` owns (kColThreads in recurrent.cu)
+_SCAN_BLOCKS: dict = {}
+
+
+def matrix_state_scan_blocks(mode: str, dk: int, dtype) -> int:
+    """How many blocks of `matrix_state_scan` (mode, key size, operand type) the device holds at a time; 0 when that
+    cannot be told. For whoever cuts long entries into segments: a launch of whole waves wastes no time on a tail."""
+    key = (mode, dk, dtype)
+    if key not in _SCAN_BLOCKS:
+        a_sm = int(library().qi_matrix_state_scan_blocks_per_sm(0 if mode == "channel_decay" else 1, int(dk), _DTYPE_CODE[dtype]))
+        _SCAN_BLOCKS[key] = max(0, a_sm) * torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _SCAN_BLOCKS[key]
 
 
 def glu_clamped(gate_up, out, limit: float, alpha: float, interleaved: bool = False) -> None:

@@ -16,7 +16,6 @@ from ..cache.manager import CacheView
 from ..cache.needs import StateNeed
 from ..errors import ConfigError
 from .base import Part, build_part, part_class, register_part
-from .norm import sum_partials
 
 
 def _floats(need) -> int:
@@ -82,10 +81,8 @@ class ParallelMixers(Part):
                                  mixer_state=self._part_of(row, beside))
             else:
                 view = CacheView(cache.entry, state=self._part_of(row, own), writes=cache.writes, mixer_state=self._part_of(row, beside))
-            outs.append(sum_partials(b.forward(x, batch, view)))      # K-split partial sums are added in 32-bit
-        if outs[0].dtype != outs[1].dtype:
-            outs = [o.to(torch.float32) for o in outs]
-        out = torch.empty(outs[0].shape, dtype=torch.float32, device=x.device)
+            outs.append(b.forward(x, batch, view))      # whole, or K-split partial sums [parts, n, h]: added in 32-bit below
+        out = torch.empty(outs[0].shape[-2:], dtype=torch.float32, device=x.device)
         kernels.scaled_sum(outs[0], outs[1], 1.0, 1.0, out)
         return out
 

@@ -41,10 +41,36 @@ def entry_segments(batch, segment: int = SEGMENT, segment_from: int = SEGMENT_FR
     return batch.extra[key]
 
 
+def segment_length(batch, blocks_a_segment: int, blocks_at_a_time: int, segment_from: int = SEGMENT_FROM) -> int:
+    """Tokens a segment for the matrix-state scan of this step: the launch has `blocks_a_segment` blocks for every segment
+    and the device holds `blocks_at_a_time` of them, so a launch lasts (waves) x (a segment's tokens, plus the few tokens'
+    worth that loading and storing a state costs); twice that for the two passes, plus the chain's walk over the
+    longest entry's segments. The cheapest multiple of 8 between 32 and 256 by that count."""
+    if blocks_at_a_time <= 0:
+        return SEGMENT
+    key = ("segment_length", blocks_a_segment, blocks_at_a_time, segment_from)
+    if key not in batch.extra:
+        q = batch.h_q_start
+        lens = [b - a for a, b in zip(q[:-1], q[1:])]
+        best = None
+        for length in range(32, 257, 8):
+            segs = [-(-n // length) if n >= segment_from else 1 for n in lens]
+            waves = -(-sum(segs) * blocks_a_segment // blocks_at_a_time)
+            cost = 2 * waves * (length + 6) + 0.5 * max(segs)
+            if best is None or cost < best[0]:
+                best = (cost, length)
+        batch.extra[key] = best[1]
+    return batch.extra[key]
+
+
 def matrix_state_scan(mode: str, r, k, v, state, o, batch, heads: int, dk: int, dv: int, **operands) -> None:
     """`kernels.matrix_state_scan` over the step's entries: in one launch, or, when an entry is long, segment by
     segment as the module's head describes. state [slots, heads, dv, dk]; o float32 [n, heads dv]."""
-    seg = entry_segments(batch)
+    if batch.extra.get("graph") or batch.max_q_len < SEGMENT_FROM:
+        seg = None
+    else:
+        col_blocks = -(-dv // kernels.MATRIX_STATE_COLUMNS)
+        seg = entry_segments(batch, segment_length(batch, heads * col_blocks, kernels.matrix_state_scan_blocks(mode, dk, r.dtype)))
     if seg is None:
         return kernels.matrix_state_scan(mode, r, k, v, state, o, batch.q_start, batch.start_pos, batch.slot_ids, heads, dk, dv, **operands)
     seg_q_start, entry_seg, zeros, ones, rows, _ = seg
