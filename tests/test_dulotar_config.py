@@ -77,3 +77,29 @@ def test_a_free_dimension_in_a_tensor_need():
     need = TensorNeed((None, 44))
     assert need.fits((5, 44)) and need.fits((16, 44)) and not need.fits((5, 40)) and not need.fits((44,))
     assert tuple(random_tensor(need, 0, 0, __import__("torch").float32).shape) == (16, 44)
+
+
+def test_segments_of_long_entries_fill_whole_waves():
+    """The length of a segment is chosen on the host from the step's entries: by the count the function's docstring gives,
+    a launch of whole waves beats one with a short tail, short entries stay whole, and without a figure for the device
+    the fixed length is used."""
+    from types import SimpleNamespace
+
+    from quantinfer_b200.parts import segments
+
+    def batch(lens):
+        q = [0]
+        for n in lens:
+            q.append(q[-1] + n)
+        return SimpleNamespace(h_q_start=q, extra={}, max_q_len=max(lens))
+
+    assert segments.segment_length(batch([2048]), 32, 0) == segments.SEGMENT
+    n = segments.segment_length(batch([2048]), 32, 888)
+    assert n % 8 == 0 and 32 <= n <= 256 and -(-2048 // n) * 32 <= 888 < -(-2048 // (n - 8)) * 32      # the shortest that still fits one wave
+    # entries below the bound count as one segment each, whatever the length
+    b = batch([100, 1, 1, 700])
+    n = segments.segment_length(b, 4, 60)
+    assert (3 + -(-700 // n)) * 4 <= 60 < (3 + -(-700 // (n - 8))) * 4
+    assert segments.segment_length(b, 4, 60) == n and len(b.extra) == 1          # kept for the step's other layers
+    # a device that holds everything at once: short segments win until the chain's walk weighs more
+    assert segments.segment_length(batch([4096]), 1, 100000) == 32

@@ -162,6 +162,17 @@ def test_the_sum_of_two_branches():
     out = torch.empty(21, 30, dtype=torch.float32, device=DEV)
     k.scaled_sum(_d(a), _d(b), 1.2, 0.5, out)
     assert float((out.cpu().double() - (1.2 * a.double() + 0.5 * b.double())).abs().max()) < 1e-6
+    # a branch may hand over the partial sums of a product whose contraction was split: three parts in 32-bit beside a whole
+    # output in bfloat16, and parts on both sides
+    parts, more = torch.randn(3, 21, 30), torch.randn(2, 21, 30)
+    k.scaled_sum(_d(parts), _d(b), 0.7, 1.0, out)
+    assert float((out.cpu().double() - (0.7 * parts.double().sum(0) + b.double())).abs().max()) < 1e-5
+    k.scaled_sum(_d(a), _d(more), 1.0, -2.0, out)
+    assert float((out.cpu().double() - (a.double() - 2.0 * more.double().sum(0))).abs().max()) < 1e-5
+    k.scaled_sum(_d(parts), _d(more), 1.0, 1.0, out)
+    assert float((out.cpu().double() - (parts.double().sum(0) + more.double().sum(0))).abs().max()) < 1e-5
+    with pytest.raises(k.KernelError):
+        k.scaled_sum(_d(parts[:, :20]), _d(b), 1.0, 1.0, out)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
