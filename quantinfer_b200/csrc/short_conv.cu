@@ -14,7 +14,7 @@
 // The state and all sums are 32-bit; inputs 32-bit or the activation type; outputs in the activation type. Weights are laid out
 // [filter][tap][channel] so that a warp's loads are contiguous.
 //
-// One thread per (token, channel). A token that stands at least taps - 1 places into its entry reads
+// One thread per token and one or four neighbouring channels. A token that stands at least taps - 1 places into its entry reads
 // only the step's own rows. The thread of an entry's FIRST token also computes the entry's next
 // taps - 2 tokens (the only ones that read the old state) and then writes the new state; the threads
 // of those tokens do nothing. So the old state is read and the new one written by the same thread, in
@@ -30,38 +30,37 @@ __device__ __forceinline__ float conv_finish(float a, const float* bias, int c, 
     return act == 1 ? a / (1.0f + expf(-a)) : a;
 }
 
+// VEC neighbouring channels of a row as one access (16 bytes of 32-bit numbers, 8 of bfloat16).
+template <typename T, int VEC>
+struct alignas(sizeof(T) * VEC) ConvPack {
+    T v[VEC];
+};
+
+template <typename T, int VEC>
+__device__ __forceinline__ void conv_load(const T* p, float (&x)[VEC]) {
+    const ConvPack<T, VEC> pk = *reinterpret_cast<const ConvPack<T, VEC>*>(p);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) x[v] = qi::to_f32<T>(pk.v[v]);
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ void conv_store(T* p, const float (&x)[VEC]) {
+    ConvPack<T, VEC> pk;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) pk.v[v] = qi::from_f32<T>(x[v]);
+    *reinterpret_cast<ConvPack<T, VEC>*>(p) = pk;
+}
+
+// The thread of an entry's first token, for channel c: the old state in registers, the entry's first taps - 1 rows (the
+// only ones that read it), then the new state.
 template <typename TI, typename TO>
-__global__ void __launch_bounds__(256)
-short_conv_kernel(const TI* __restrict__ h, long long ldh, const float* __restrict__ bias, int act,
-                  const float* __restrict__ w, float* __restrict__ state,
-                  TO* __restrict__ out0, TO* __restrict__ out1, TO* __restrict__ copy,
-                  const int* __restrict__ token_req, const int* __restrict__ q_start,
-                  const int* __restrict__ start_pos, const int* __restrict__ slot_ids, int n_tokens, int C,
-                  int taps, int n_filters, int residual, long long state_stride) {
-    qi::pdl_wait();
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)n_tokens * C) return;
-    const int t = (int)(idx / C), c = (int)(idx % C);
-    const int e = token_req[t];
-    const int first = q_start[e];
-    const int i = t - first;
-    const float x = qi::to_f32<TI>(h[(size_t)t * ldh + c]);
-    if (copy) copy[idx] = qi::from_f32<TO>(x);
+__device__ __forceinline__ void conv_entry_head(const TI* __restrict__ h, long long ldh, const float* __restrict__ bias, int act,
+                                                const float* __restrict__ w, float* __restrict__ state, TO* __restrict__ out0,
+                                                TO* __restrict__ out1, const int* __restrict__ q_start,
+                                                const int* __restrict__ start_pos, const int* __restrict__ slot_ids, int e, int first,
+                                                int c, int C, int taps, int n_filters, int residual, long long state_stride) {
     const int back = taps - 1;
     const float* w1 = w + (size_t)taps * C;
-    if (i >= back) {
-        float a0 = residual ? x : 0.f, a1 = a0;
-        for (int j = 0; j < taps; ++j) {
-            const float v = qi::to_f32<TI>(h[(size_t)(t - back + j) * ldh + c]);
-            a0 = fmaf(w[(size_t)j * C + c], v, a0);
-            if (n_filters > 1) a1 = fmaf(w1[(size_t)j * C + c], v, a1);
-        }
-        out0[idx] = qi::from_f32<TO>(conv_finish(a0, bias, c, act));
-        if (n_filters > 1) out1[idx] = qi::from_f32<TO>(conv_finish(a1, bias ? bias + C : nullptr, c, act));
-        return;
-    }
-    if (i != 0) return;
-    // the entry's first token: old state in registers, the first rows, then the new state
     const int len = q_start[e + 1] - first;
     const int p0 = start_pos[e];
     float* st = state + (size_t)slot_ids[e] * state_stride + c;
@@ -103,6 +102,65 @@ short_conv_kernel(const TI* __restrict__ h, long long ldh, const float* __restri
     }
 }
 
+// One thread per token and VEC neighbouring channels (VEC 4 where the rows' lengths and addresses allow 16-byte accesses).
+template <typename TI, typename TO, int VEC>
+__global__ void __launch_bounds__(256)
+short_conv_kernel(const TI* __restrict__ h, long long ldh, const float* __restrict__ bias, int act,
+                  const float* __restrict__ w, float* __restrict__ state,
+                  TO* __restrict__ out0, TO* __restrict__ out1, TO* __restrict__ copy,
+                  const int* __restrict__ token_req, const int* __restrict__ q_start,
+                  const int* __restrict__ start_pos, const int* __restrict__ slot_ids, int n_tokens, int C,
+                  int taps, int n_filters, int residual, long long state_stride) {
+    qi::pdl_wait();
+    const int CV = C / VEC;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_tokens * CV) return;
+    const int t = (int)(idx / CV), c = (int)(idx % CV) * VEC;
+    const int e = token_req[t];
+    const int first = q_start[e];
+    const int i = t - first;
+    float x[VEC];
+    conv_load<TI, VEC>(h + (size_t)t * ldh + c, x);
+    if (copy) conv_store<TO, VEC>(copy + (size_t)t * C + c, x);
+    const int back = taps - 1;
+    if (i >= back) {
+        const float* w1 = w + (size_t)taps * C;
+        float a0[VEC], a1[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) a0[v] = a1[v] = residual ? x[v] : 0.f;
+        for (int j = 0; j < taps; ++j) {
+            float hv[VEC], wv[VEC];
+            if (j == back) {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) hv[v] = x[v];
+            } else {
+                conv_load<TI, VEC>(h + (size_t)(t - back + j) * ldh + c, hv);
+            }
+            conv_load<float, VEC>(w + (size_t)j * C + c, wv);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) a0[v] = fmaf(wv[v], hv[v], a0[v]);
+            if (n_filters > 1) {
+                conv_load<float, VEC>(w1 + (size_t)j * C + c, wv);
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) a1[v] = fmaf(wv[v], hv[v], a1[v]);
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) a0[v] = conv_finish(a0[v], bias, c + v, act);
+        conv_store<TO, VEC>(out0 + (size_t)t * C + c, a0);
+        if (n_filters > 1) {
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) a1[v] = conv_finish(a1[v], bias ? bias + C : nullptr, c + v, act);
+            conv_store<TO, VEC>(out1 + (size_t)t * C + c, a1);
+        }
+        return;
+    }
+    if (i != 0) return;
+    for (int v = 0; v < VEC; ++v)
+        conv_entry_head<TI, TO>(h, ldh, bias, act, w, state, out0, out1, q_start, start_pos, slot_ids, e, first, c + v, C, taps, n_filters,
+                                residual, state_stride);
+}
+
 }  // namespace
 
 // h [n_tokens, C] in `in_dtype` with `ldh` elements from row to row; bias float32 [n_filters, C] or null; act 0: none,
@@ -121,14 +179,22 @@ extern "C" int qi_short_conv(const void* h, int in_dtype, long long ldh, const f
     QI_REQUIRE(out0 && (n_filters == 1 || out1), "short_conv: an output is missing");
     QI_REQUIRE(act == 0 || act == 1, "short_conv: unknown activation code %d", act);
     if (n_tokens == 0) return 0;
-    const size_t total = (size_t)n_tokens * channels;
+    // four channels a thread where every row of every operand starts on a 16-byte boundary (8 for bfloat16)
+    auto aligned = [](const void* p, size_t bytes) { return p == nullptr || reinterpret_cast<size_t>(p) % bytes == 0; };
+    const size_t in_bytes = (in_dtype == qi::kF32 ? 4 : 2) * 4, out_bytes = (out_dtype == qi::kF32 ? 4 : 2) * 4;
+    const bool wide = channels % 4 == 0 && ldh % 4 == 0 && aligned(h, in_bytes) && aligned(w, 16) && aligned(out0, out_bytes) &&
+                      aligned(out1, out_bytes) && aligned(copy, out_bytes);
+    const size_t total = (size_t)n_tokens * (wide ? channels / 4 : channels);
     QI_REQUIRE((total + 255) / 256 <= 0x7fffffffull, "short_conv: grid too large");
+#define QI_CONV(VEC)                                                                                                                  \
+    qi::launch(short_conv_kernel<TI, TO, VEC>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const TI*)h, ldh, bias, act, \
+               w, state, (TO*)out0, (TO*)out1, (TO*)copy, token_req, q_start, start_pos, slot_ids, n_tokens, channels, taps, n_filters,   \
+               residual, state_stride)
     QI_DISPATCH_DTYPE(in_dtype, TI, {
         QI_DISPATCH_DTYPE(out_dtype, TO, {
-            qi::launch(short_conv_kernel<TI, TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const TI*)h, ldh, bias, act,
-                       w, state, (TO*)out0, (TO*)out1, (TO*)copy, token_req, q_start, start_pos, slot_ids, n_tokens, channels, taps,
-                       n_filters, residual, state_stride);
+            if (wide) QI_CONV(4); else QI_CONV(1);
         });
     });
+#undef QI_CONV
     return qi::check_launch("short_conv");
 }
