@@ -322,6 +322,58 @@ __global__ void add_layernorm_kernel(float* __restrict__ resid, const TD* __rest
     }
 }
 
+// The same with a row in registers: eight neighbouring coordinates a thread (rows of up to 8 x blockDim), every operand
+// read once in 16- and 32-byte accesses, the mean and the deviations' squares from the registers. A CTA takes rows
+// blockIdx.x, blockIdx.x + gridDim.x, ...
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(512, 3) add_layernorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                         int delta_splits, size_t delta_split_stride, const float* __restrict__ gain,
+                                         const float* __restrict__ bias, float eps, TO* __restrict__ out,
+                                         const int* __restrict__ rows, int hidden, int write_resid, int n_rows) {
+    __shared__ float scratch[32];
+    qi::pdl_wait();
+    const int i = threadIdx.x * 8;
+    const bool active = i < hidden;
+    for (int r = blockIdx.x; r < n_rows; r += gridDim.x) {
+        const int s = rows ? rows[r] : r;
+        float* xr = resid + (size_t)s * hidden;
+        const TD* dr = delta ? delta + (size_t)s * hidden : nullptr;
+        float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, d[8], g[8], b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (active) {
+            Vec8<float>::load(xr + i, x);
+            Vec8<float>::load(gain + i, g);
+            if (bias) Vec8<float>::load(bias + i, b);
+            if (dr) {
+#pragma unroll 4
+                for (int k = 0; k < delta_splits; ++k) {
+                    Vec8<TD>::load(dr + k * delta_split_stride + i, d);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) x[j] += d[j];
+                }
+            }
+            if (write_resid) Vec8<float>::store(xr + i, x);
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum += x[j];
+        const float mean = qi::block_sum(sum, scratch) / (float)hidden;
+        float sq = 0.f;
+        if (active) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                x[j] -= mean;
+                sq = fmaf(x[j], x[j], sq);
+            }
+        }
+        const float inv = 1.0f / sqrtf(qi::block_sum(sq, scratch) / (float)hidden + eps);
+        if (active) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = fmaf(x[j] * inv, g[j], b[j]);
+            Vec8<TO>::store(out + (size_t)r * hidden + i, x);
+        }
+    }
+}
+
 int pick_threads(int hidden) { return hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : (hidden >= 128 ? 128 : 32)); }
 
 }  // namespace
@@ -392,6 +444,27 @@ extern "C" int qi_add_layernorm(float* resid, const void* delta, int delta_dtype
     QI_REQUIRE(eps > 0.f, "add_layernorm: eps must be positive");
     if (n_rows == 0) return 0;
     const int dd = delta ? delta_dtype : qi::kF32;
+    const bool vec = hidden % 8 == 0 && hidden <= 4096 && ((uintptr_t)resid & 31) == 0 && ((uintptr_t)delta & 15) == 0 &&
+                     ((uintptr_t)out & 15) == 0 && ((uintptr_t)gain & 15) == 0 && ((uintptr_t)bias & 15) == 0 &&
+                     delta_split_stride % 8 == 0;
+    if (vec) {
+        const int threads = (hidden / 8 + 31) / 32 * 32;
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        }
+        const int resident = sms * (1536 / threads < 16 ? 1536 / threads : 16);      // three CTAs of 512 threads an SM, or as many smaller ones
+        const int grid = n_rows < resident ? n_rows : resident;
+        QI_DISPATCH_DTYPE(dd, TD, {
+            QI_DISPATCH_DTYPE(out_dtype, TO, {
+                qi::launch(add_layernorm_vec_kernel<TD, TO>, dim3(grid), dim3(threads), 0, stream, resid, (const TD*)delta, delta_splits,
+                           (size_t)delta_split_stride, gain, bias, eps, (TO*)out, rows, hidden, write_resid, n_rows);
+            });
+        });
+        return qi::check_launch("add_layernorm");
+    }
     const int threads = pick_threads(hidden);
     QI_DISPATCH_DTYPE(dd, TD, {
         QI_DISPATCH_DTYPE(out_dtype, TO, {
