@@ -649,7 +649,7 @@ def compare_kiruvik(args, title="Kiruvik layers beside dense GQA (Qwen3) layers 
                 # a prompt step with a class left out runs its other kernels on whatever the buffers hold; a router then
                 # sends every token to the same few experts and the step gets SLOWER: such a difference says nothing and
                 # is left out (the kernels' own times are in profiles/)
-                left = pre_ms - p_without if pre_ms > p_without else None
+                left = pre_ms - p_without if pre_ms - p_without > 0.01 * pre_ms else None       # (below a hundredth of the step: noise)
                 c = {"decode_alone_ms": round(d_alone, 4), "prefill_left_out_ms": round(left, 4) if left is not None else None}
                 if d_alone > 0:
                     c["decode_frac_hbm"] = round(work[cls][0] / (d_alone * 1e-3) / 1e9 / hbm, 4)

@@ -179,10 +179,12 @@ extern "C" int qi_short_conv(const void* h, int in_dtype, long long ldh, const f
     QI_REQUIRE(out0 && (n_filters == 1 || out1), "short_conv: an output is missing");
     QI_REQUIRE(act == 0 || act == 1, "short_conv: unknown activation code %d", act);
     if (n_tokens == 0) return 0;
-    // four channels a thread where every row of every operand starts on a 16-byte boundary (8 for bfloat16)
+    // four channels a thread where every row of every operand starts on a 16-byte boundary (8 for bfloat16) and the step
+    // has rows enough to fill the device so; a step of few rows (single tokens, each the first of its entry, whose thread
+    // walks the old state) keeps a thread a channel. Both forms add in the same order: a row's result is the same.
     auto aligned = [](const void* p, size_t bytes) { return p == nullptr || reinterpret_cast<size_t>(p) % bytes == 0; };
     const size_t in_bytes = (in_dtype == qi::kF32 ? 4 : 2) * 4, out_bytes = (out_dtype == qi::kF32 ? 4 : 2) * 4;
-    const bool wide = channels % 4 == 0 && ldh % 4 == 0 && aligned(h, in_bytes) && aligned(w, 16) && aligned(out0, out_bytes) &&
+    const bool wide = n_tokens >= 256 && channels % 4 == 0 && ldh % 4 == 0 && aligned(h, in_bytes) && aligned(w, 16) && aligned(out0, out_bytes) &&
                       aligned(out1, out_bytes) && aligned(copy, out_bytes);
     const size_t total = (size_t)n_tokens * (wide ? channels / 4 : channels);
     QI_REQUIRE((total + 255) / 256 <= 0x7fffffffull, "short_conv: grid too large");

@@ -12,7 +12,7 @@ import torch
 
 from .. import kernels
 
-SEGMENT = 64          # tokens a segment of a long entry
+SEGMENT = 64          # tokens a segment of a long entry, where nothing better is known (`segment_length` picks one a step)
 SEGMENT_FROM = 192    # entries shorter than this run in one piece
 
 

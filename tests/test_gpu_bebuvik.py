@@ -132,6 +132,49 @@ def test_short_conv_in_portions_of_every_size(taps, dtype):
             done[s] += n
 
 
+@pytest.mark.parametrize("taps", [1, 3, 4])
+@pytest.mark.parametrize("in_dtype, dtype", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16), (torch.bfloat16, torch.bfloat16)])
+def test_short_conv_with_four_channels_a_thread(taps, in_dtype, dtype):
+    """A step of 256 rows and more, with a channel count that is a multiple of four, takes the form with 16-byte
+    accesses; the same rows in steps of fewer take the form with a thread a channel. Both must give the same bits, and
+    the formula's values: three requests in one launch (one continues a sequence whose state an earlier step left, one
+    is a single token, one starts at zero over a stale slot), two filters, a copy of the input."""
+    from quantinfer_b200 import kernels
+
+    torch.manual_seed(taps + 10)
+    ch = 40
+    w = torch.randn(2, ch, taps)
+    wd = w.permute(0, 2, 1).contiguous().to(DEV)
+    seqs = {2: torch.randn(30 + 200, ch).to(in_dtype).float(), 0: torch.randn(5 + 1, ch).to(in_dtype).float(), 1: torch.randn(90, ch).to(in_dtype).float()}
+    want = {s: [x + plain.causal_conv(x, w[k]) for k in range(2)] for s, x in seqs.items()}
+    results = []
+    for big in (True, False):
+        state = torch.full((3, max(taps - 1, 1), ch), 7.0, device=DEV)[:, :taps - 1].contiguous()
+        got = {s: [[], []] for s in seqs}
+        # first the beginnings of requests 2 and 0 (their state stays behind), then the step of 291 rows, whole or in pieces
+        plan = [[(2, 0, 30), (0, 0, 5)]] + ([[(2, 30, 200), (0, 5, 1), (1, 0, 90)]] if big else
+                                            [[(2, 30, 100), (0, 5, 1), (1, 0, 50)], [(2, 130, 100), (1, 50, 40)]])
+        for group in plan:
+            lengths, starts = [n for _, _, n in group], [a for _, a, _ in group]
+            h = torch.cat([seqs[s][a:a + n] for s, a, n in group]).to(in_dtype).to(DEV)
+            q_start, token_req, _, start_pos, slots = _state_batch(lengths, starts, [s for s, _, _ in group])
+            outs = [torch.empty(h.shape, dtype=dtype, device=DEV) for _ in range(2)]
+            copy = torch.empty(h.shape, dtype=dtype, device=DEV)
+            kernels.short_conv(h, wd, state if taps > 1 else None, outs, copy, token_req, q_start, start_pos, slots)
+            assert torch.equal(copy.float().cpu(), h.float().cpu().to(dtype).float())
+            at = 0
+            for s, a, n in group:
+                for k in range(2):
+                    got[s][k].append(outs[k][at:at + n].float().cpu())
+                at += n
+        results.append({s: [torch.cat(g) for g in gs] for s, gs in got.items()})
+    for s in seqs:
+        for k in range(2):
+            assert torch.equal(results[0][s][k], results[1][s][k]), (s, k)
+            err = float((results[0][s][k] - want[s][k]).abs().max())
+            assert err < (2e-5 if dtype == torch.float32 else 0.06), (s, k, err)
+
+
 def test_small_kernels_against_their_formulas():
     from quantinfer_b200 import kernels
 

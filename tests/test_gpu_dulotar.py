@@ -611,6 +611,23 @@ def test_replay_family(models, name, dtype, family):
     _compare(got, _expect(models, name), name, dtype, family)
 
 
+def test_a_two_branch_layer_that_runs_twice_with_one_layer_s_weights(tmp_path):
+    """The second call has pages, filter rows and a matrix state of its own: with shared ones, the keys the second call
+    writes would be read by the first in the next step. Portions down to two tokens, then a mixed batch on a small pool."""
+    both = dict(l=left(4, 2, 16, 8, rot_dims=8, chunk=24, conv=3, softcap=5.0), r=right(2, 8, 16, (0.9, 0.99)), left_scale=1.1, right_scale=0.7, ff=48)
+    cfg = model(150, 40, 1e-5, 3.0, 3, [parallel(**both), mingru(24), parallel(**both, weights_of=0), wkv(2, 8, rank=4), parallel(**both, weights_of=0)])
+    w = draw_weights(cfg, 7)
+    folder = write_folder(tmp_path / "twice", cfg, w)
+    reqs = {f"t{i}": random_tokens(n, 150, seed=70 + i) for i, n in enumerate([90, 40, 70, 33, 58])}
+    expect = plain_rows(clean(cfg), w, reqs)
+    mixed, peak = mixed_trace(reqs, seed=3, max_live=4, max_tokens=round64(90) + 128)
+    for steps, max_tokens in ((portions_trace(reqs), round64(90)), (mixed, peak)):
+        got = run_trace_engine(folder, "float32", steps, max_tokens, 8)
+        assert set(got) == set(expect)
+        worst = max(float(np.abs(got[k].astype(np.float64) - expect[k].astype(np.float64)).max()) for k in expect)
+        assert worst <= TOL_F32, worst
+
+
 def test_the_cuts_agree_with_one_another_in_float32(models):
     """What a position's logits are must not depend on how its prompt was cut or on its company in the batch."""
     folder, cfg, w = models["U"]
