@@ -4,10 +4,12 @@ from .registry import (architectures, config_class_for, config_from_dict, load_c
 from .bebuvik import BebuvikConfig
 from .kiruvik import KiruvikConfig
 from .dulotar import DulotarConfig
+from .lemotar import LemotarConfig
 from .spec import (AttentionSpec, BigramEmbeddingSpec, DenseFeedForwardSpec, EmbeddingSpec, FeedForwardSpec, HeadSpec,
                    LatentAttentionSpec, LayerCall, LayerSpec, ModelSpec, NormSpec, ParallelLayerSpec, PositionSpec,
                    RotarySpec, ShortConvSpec, ClampedGLUSpec, GatedAttentionSpec, MoESpec, ReentrySpec, SandwichLayerSpec,
-                   StateSpaceSpec, ConvPreNormLayerSpec, LightningAttentionSpec, MinGRUSpec, ParallelMixersSpec, TimeMixSpec)
+                   StateSpaceSpec, ConvPreNormLayerSpec, LightningAttentionSpec, MinGRUSpec, ParallelMixersSpec, TimeMixSpec,
+                   GatedDeltaSpec, PostNormLayerSpec)
 
 __all__ = [
     "Qwen3Config", "architectures", "config_class_for", "config_from_dict", "load_config",
@@ -16,4 +18,5 @@ __all__ = [
     "DenseFeedForwardSpec", "LatentAttentionSpec", "ParallelLayerSpec", "RotarySpec", "ShortConvSpec",
     "KiruvikConfig", "ClampedGLUSpec", "GatedAttentionSpec", "MoESpec", "ReentrySpec", "SandwichLayerSpec", "StateSpaceSpec",
     "DulotarConfig", "ConvPreNormLayerSpec", "LightningAttentionSpec", "MinGRUSpec", "ParallelMixersSpec", "TimeMixSpec",
+    "LemotarConfig", "GatedDeltaSpec", "PostNormLayerSpec",
 ]

@@ -79,6 +79,9 @@ def _register_builtin() -> None:
     from .dulotar import ARCHITECTURE as DULOTAR, DulotarConfig
 
     register_architecture(DULOTAR, DulotarConfig)
+    from .lemotar import ARCHITECTURE as LEMOTAR, LemotarConfig
+
+    register_architecture(LEMOTAR, LemotarConfig)
 
 
 _register_builtin()

@@ -86,6 +86,10 @@ class RotarySpec:
     theta: float
     pairing: str = "interleaved"
     kind: str = "rope_direct"
+    stretch: Optional[tuple] = None   # (factor, original, fast, slow): pairs that turn fewer than `slow` times over
+                                      # `original` positions have their frequency divided by `factor`, pairs that turn
+                                      # more than `fast` times keep it, a linear ramp over the pair's number lies
+                                      # between (YaRN); cos and sin are then multiplied by 0.1 ln(factor) + 1
 
 
 @dataclass(frozen=True)
@@ -110,6 +114,7 @@ class LatentAttentionSpec:
     shares_latent: bool = False
     prefix: str = ""
     kind: str = "latent_attention"
+    out_gate: bool = False            # the concatenated heads are multiplied by sigmoid(W_g x) (`g`) before the output projection
 
 
 @dataclass(frozen=True)
@@ -198,6 +203,13 @@ class GatedAttentionSpec:
                                        # n - 1 projected rows are a request's state
     softcap: Optional[float] = None    # c: a score s becomes c tanh(s / c) before the softmax
     out_scale: float = 1.0             # a factor on what the mixer hands on (applied before the output projection)
+    sink: Optional[str] = None         # the softmax's denominator holds one more term exp(b_h) a head, with no key and no
+                                       # value: "zero": b_h = 0 (one is added); "learned": b is the tensor `sink` [heads]
+    values_from_keys: bool = False     # there is no `v`: a position's value is its key as projected (before any norm and
+                                       # rotation), so value_dim equals head_dim
+    qk_norm: Optional[str] = None      # "whole": q (all heads at once) and k (likewise) each pass one RMS norm over the whole
+                                       # projection before the rotation, gains `q.norm` [heads head_dim], `k.norm`
+    qk_norm_eps: float = 1e-6
 
 
 @dataclass(frozen=True)
@@ -251,12 +263,54 @@ class LightningAttentionSpec:
 @dataclass(frozen=True)
 class ParallelMixersSpec:
     """Two mixers side by side that read the same input; their outputs are added. Each branch's own factor is a field of
-    its spec (`out_scale`). At most one branch keeps pages; every other state is of fixed size."""
+    its spec (`out_scale`). At most one branch keeps pages; every other state is of fixed size. `out_norm_names`
+    (left, right): each branch's output first passes an RMS norm over the model width with the gain of that name (eps
+    `out_norm_eps`); `sum_scale` multiplies the sum."""
 
     left: object
     right: object
     prefix: str = ""
     kind: str = "parallel_mixers"
+    out_norm_names: Optional[tuple] = None
+    out_norm_eps: float = 1e-6
+    sum_scale: float = 1.0
+    hidden_size: Optional[int] = None  # needed with `out_norm_names` (the gains' size)
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """A matrix state per head that is decayed per key channel and corrected towards each token's value (gated delta
+    rule). q, k = projections to `kv_heads` x `head_dim`, v to `heads` x `value_dim` (head h reads q/k head
+    floor(h / (heads / kv_heads))); each passes a causal convolution of `conv_taps` taps per channel (`q.conv` ...,
+    no bias) and silu; q and k become unit vectors per head (x / sqrt(sum x^2 + `unit_eps`)), q times head_dim^(-1/2);
+    beta = sigmoid(W_b x) a head; decay = exp(-exp(A_log_h) softplus(W_a2 W_a1 x + dt_bias)) per head and key
+    channel; S <- diag(decay) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; every head's o over its root mean
+    square (eps `norm_eps`) times `norm` [value_dim] times sigmoid(W_g2 W_g1 x); W_o. The ranks of the two low-rank
+    pairs are read from `a1` and `g1`. State (32-bit): S, and the convolutions' last taps - 1 inputs."""
+
+    hidden_size: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    value_dim: int
+    conv_taps: int
+    norm_eps: float
+    unit_eps: float = 1e-6
+    prefix: str = ""
+    kind: str = "gated_delta"
+
+
+@dataclass(frozen=True)
+class PostNormLayerSpec:
+    """The block whose norms come after the sums: x <- norm1(alpha x + mixer(x)); x <- norm2(alpha x + ffn(x)). The
+    sublayers read the stream itself. `ffn` (with its norm) may be None."""
+
+    mixer_norm: NormSpec
+    mixer: object
+    ffn_norm: Optional[NormSpec]
+    ffn: object
+    alpha: float = 1.0
+    kind: str = "postnorm"
 
 
 @dataclass(frozen=True)

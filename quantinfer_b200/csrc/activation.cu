@@ -101,6 +101,17 @@ __global__ void gated_sum_kernel(const TG* __restrict__ gates, int ldg, const fl
     }
 }
 
+// x[t, c] *= sigmoid(gate[t, c]) in place; the gate's rows lie `ldg` elements apart.
+template <typename T, typename TG>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, const TG* __restrict__ gate, long long ldg, int n_tokens, int C) {
+    qi::pdl_wait();
+    const size_t total = (size_t)n_tokens * C;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / C, c = idx % C;
+        x[idx] = qi::from_f32<T>(qi::to_f32<T>(x[idx]) / (1.0f + expf(-qi::to_f32<TG>(gate[t * ldg + c]))));
+    }
+}
+
 __global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap, float inv_cap) {
     qi::pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
@@ -154,6 +165,20 @@ extern "C" int qi_gated_sum(const void* gates, int gates_dtype, int ldg, const f
 }
 
 // x = cap * tanh(x / cap) in place, float32 [n].
+// x [n, C] in `dtype`, multiplied in place by sigmoid(gate), gate [n, >= C] in `gate_dtype` with rows `ldg` elements apart.
+extern "C" int qi_sigmoid_gate(void* x, int dtype, const void* gate, int gate_dtype, long long ldg, int n_tokens, int C,
+                               cudaStream_t stream) {
+    QI_REQUIRE(n_tokens >= 0 && C > 0 && ldg >= C, "sigmoid_gate: bad sizes");
+    if (n_tokens == 0) return 0;
+    const size_t total = (size_t)n_tokens * C;
+    QI_DISPATCH_DTYPE(dtype, T, {
+        QI_DISPATCH_DTYPE(gate_dtype, TG, {
+            qi::launch(sigmoid_gate_kernel<T, TG>, dim3(blocks_for(total)), dim3(256), 0, stream, (T*)x, (const TG*)gate, ldg, n_tokens, C);
+        });
+    });
+    return qi::check_launch("sigmoid_gate");
+}
+
 extern "C" int qi_softcap(float* x, long long n, float cap, cudaStream_t stream) {
     QI_REQUIRE(n >= 0 && cap > 0.f, "softcap: bad size or cap");
     if (n == 0) return 0;

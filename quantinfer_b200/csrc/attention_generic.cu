@@ -37,7 +37,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
                          int max_blocks, int page_size, int num_pages,
                          const int* __restrict__ positions, const int* __restrict__ token_req,
                          int nq, int nkv, int d, int dv, float scale, float softcap, float out_scale, int window, int chunk,
-                         const T* __restrict__ gate, long long ldg, int* __restrict__ status) {
+                         const T* __restrict__ gate, long long ldg, const float* __restrict__ sink, int* __restrict__ status) {
     extern __shared__ float smem[];
     float* q_s = smem;                          // [d]
     float* part_acc = smem + d;                 // [kWarps][dv]
@@ -116,7 +116,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
     }
     __syncthreads();
 
-    float gm = -INFINITY;
+    float gm = sink ? sink[h] : -INFINITY;      // the sink: one more term in the denominator, with no key and no value
     for (int w = 0; w < kWarps; ++w) gm = fmaxf(gm, part_m[w]);
     float gl = 0.f;
     float wscale[kWarps];
@@ -124,6 +124,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
         wscale[w] = (part_m[w] == -INFINITY) ? 0.f : expf(part_m[w] - gm);
         gl += part_l[w] * wscale[w];
     }
+    if (sink) gl += expf(sink[h] - gm);
     T* orow = out + ((size_t)t * nq + h) * dv;
     const T* grow = gate ? gate + (size_t)t * ldg + (size_t)h * dv : nullptr;
     for (int i = threadIdx.x; i < dv; i += blockDim.x) {
@@ -141,12 +142,13 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
 // q [n, nq d]; out [n, nq dv]; k_pages [pages, nkv, page_size, d]; v_pages [pages, nkv, page_size, dv];
 // window 0: no window; chunk 0: no chunks; gate (may be null): row t, head h, element i at gate[t * ldg + h * dv + i];
 // softcap c > 0: a score s becomes c tanh(s / c) before the softmax (0: scores as they are); out_scale multiplies the result.
-extern "C" int qi_attention_generic_cap(const void* q, void* out, int dtype, const void* k_pages,
+// sink (may be null): float32 [nq]; the softmax's denominator of head h holds exp(sink[h]) once more.
+extern "C" int qi_attention_generic_sink(const void* q, void* out, int dtype, const void* k_pages,
                                        const void* v_pages, const int* block_table, int max_blocks,
                                        int page_size, int num_pages, const int* positions,
                                        const int* token_req, int n_tokens, int nq, int nkv, int d, int dv,
                                        float scale, float softcap, float out_scale, int window, int chunk, const void* gate,
-                                       long long ldg, int* status, cudaStream_t stream) {
+                                       long long ldg, const float* sink, int* status, cudaStream_t stream) {
     QI_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0 && dv > 0, "attention: bad sizes");
     QI_REQUIRE(nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
     QI_REQUIRE(d <= kMaxD && dv <= kMaxD, "attention: head sizes %d / %d are above the limit %d of this kernel", d, dv, kMaxD);
@@ -166,10 +168,21 @@ extern "C" int qi_attention_generic_cap(const void* q, void* out, int dtype, con
                 (const T*)q + (size_t)t0 * nq * d, (T*)out + (size_t)t0 * nq * dv, (const T*)k_pages,
                 (const T*)v_pages, block_table, max_blocks, page_size, num_pages, positions + t0,
                 token_req + t0, nq, nkv, d, dv, scale, softcap, out_scale, window, chunk,
-                gate ? (const T*)gate + (size_t)t0 * ldg : (const T*)nullptr, ldg, status);
+                gate ? (const T*)gate + (size_t)t0 * ldg : (const T*)nullptr, ldg, sink, status);
         });
     }
     return qi::check_launch("attention_generic");
+}
+
+extern "C" int qi_attention_generic_cap(const void* q, void* out, int dtype, const void* k_pages,
+                                       const void* v_pages, const int* block_table, int max_blocks,
+                                       int page_size, int num_pages, const int* positions,
+                                       const int* token_req, int n_tokens, int nq, int nkv, int d, int dv,
+                                       float scale, float softcap, float out_scale, int window, int chunk, const void* gate,
+                                       long long ldg, int* status, cudaStream_t stream) {
+    return qi_attention_generic_sink(q, out, dtype, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, positions,
+                                     token_req, n_tokens, nq, nkv, d, dv, scale, softcap, out_scale, window, chunk, gate, ldg,
+                                     nullptr, status, stream);
 }
 
 extern "C" int qi_attention_generic_ex(const void* q, void* out, int dtype, const void* k_pages,

@@ -264,7 +264,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                       float scale_log2e, int window, int* __restrict__ status, int n_ranges,
                                       float* __restrict__ ws_o, float* __restrict__ ws_ml, int chunk,
                                       const qi::bf16* __restrict__ gate, long long ldg, float cap, float cap_pre,
-                                      float out_scale) {
+                                      float out_scale, const float* __restrict__ sink) {
     extern __shared__ uint8_t smem_raw[];
     using B = Bars;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -553,6 +553,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
         } else if (ok) {
             tc_fence_after();
+            // the sink: exp(sink_h) once more in the denominator (m is a base-2 exponent); with key ranges the merge adds it
+            if (sink && m != -INFINITY) l += ex2(sink[h] * 1.4426950408889634f - m);
             const float inv = l > 0.f ? out_scale / l : 0.f;
             qi::bf16* orow = out + ((size_t)(q0 + row) * nq + h) * D;
             const qi::bf16* grow = gate ? gate + (size_t)(q0 + row) * ldg + (size_t)h * D : nullptr;
@@ -595,13 +597,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 // out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M) over the key ranges of a query row, in range order.
 __global__ void attention_prefill_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                                qi::bf16* __restrict__ out, int nq, int n_ranges,
-                                               const qi::bf16* __restrict__ gate, long long ldg, float out_scale) {
+                                               const qi::bf16* __restrict__ gate, long long ldg, float out_scale,
+                                               const float* __restrict__ sink) {
     qi::pdl_enter();
     const int h = blockIdx.x;
     const size_t t = blockIdx.y;
     const size_t base = (t * nq + h) * n_ranges;
     float M = -INFINITY;
     for (int s = 0; s < n_ranges; ++s) M = fmaxf(M, ws_ml[(base + s) * 2]);
+    const float sink_term = (sink && M != -INFINITY) ? exp2f(sink[h] * 1.4426950408889634f - M) : 0.f;
     for (int col = threadIdx.x; col < D; col += blockDim.x) {
         float L = 0.f, O = 0.f;
         for (int s = 0; s < n_ranges; ++s) {
@@ -611,6 +615,7 @@ __global__ void attention_prefill_merge_kernel(const float* __restrict__ ws_o, c
             L += ws_ml[(base + s) * 2 + 1] * f;
             O += ws_o[(base + s) * D + col] * f;
         }
+        L += sink_term;
         float o = L > 0.f ? O / L * out_scale : 0.f;
         if (gate) o = o / (1.f + __expf(-__bfloat162float(gate[t * (size_t)ldg + (size_t)h * D + col])));
         out[(t * nq + h) * D + col] = __float2bfloat16_rn(o);
@@ -665,14 +670,15 @@ extern "C" int qi_attention_prefill_tcgen05_supported(int nq, int nkv, int d, in
 // `workspace` must then hold n_tokens * nq * n_ranges * (128 + 2) floats. chunk > 0: a query at position i sees
 // key j <= i only if floor(i / chunk) = floor(j / chunk). gate (or null): bfloat16 [n_tokens, nq * 128] with rows
 // `ldg` elements apart; the output is multiplied element by element with its sigmoid. softcap c > 0: a score s (scale
-// applied) becomes c tanh(s / c) before the softmax. out_scale multiplies the result.
-extern "C" int qi_attention_prefill_tcgen05_ex(const void* q, void* out, const void* k_pages, const void* v_pages,
+// applied) becomes c tanh(s / c) before the softmax. out_scale multiplies the result. sink (or null): float32 [nq]; the
+// softmax's denominator of head h holds exp(sink[h]) once more.
+extern "C" int qi_attention_prefill_tcgen05_sink(const void* q, void* out, const void* k_pages, const void* v_pages,
                                                const int* block_table, int max_blocks, int page_size, int num_pages,
                                                const int* q_start, const int* start_pos, const int* tile_req,
                                                const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int d,
                                                float scale, int window, int chunk, const void* gate, long long ldg,
                                                int n_ranges, float* workspace, int* status, float softcap, float out_scale,
-                                               cudaStream_t stream) {
+                                               const float* sink, cudaStream_t stream) {
     QI_REQUIRE(softcap >= 0.f && scale > 0.f, "attention_prefill_tcgen05: the soft cap must be >= 0 (0 = none) and the scale positive");
     QI_REQUIRE(chunk >= 0 && (!gate || (((uintptr_t)gate & 15) == 0 && ldg % 8 == 0 && ldg >= (long long)nq * D)),
                "attention_prefill_tcgen05: a gate must be 16-byte aligned with rows a multiple of 8 elements apart");
@@ -706,14 +712,26 @@ extern "C" int qi_attention_prefill_tcgen05_ex(const void* q, void* out, const v
     qi::launch(attention_prefill_tcgen05_kernel, dim3(nq, n_tiles, n_ranges), dim3(kThreads), kSmemBytes, stream, mq, mk, mv,
                (qi::bf16*)out, block_table, max_blocks, page_size, box_rows, num_pages, q_start, start_pos, tile_req,
                tile_q0, nq, nkv, softcap > 0.f ? log2e : scale * log2e, window, status, n_ranges, ws_o, ws_ml, chunk,
-               (const qi::bf16*)gate, ldg, softcap, cap_pre, out_scale);
+               (const qi::bf16*)gate, ldg, softcap, cap_pre, out_scale, sink);
     if (n_ranges > 1) {
         if (int rc = qi::check_launch("attention_prefill_tcgen05")) return rc;
         qi::launch(attention_prefill_merge_kernel, dim3(nq, n_tokens), dim3(128), 0, stream, (const float*)ws_o,
-                   (const float*)ws_ml, (qi::bf16*)out, nq, n_ranges, (const qi::bf16*)gate, ldg, out_scale);
+                   (const float*)ws_ml, (qi::bf16*)out, nq, n_ranges, (const qi::bf16*)gate, ldg, out_scale, sink);
         return qi::check_launch("attention_prefill_merge");
     }
     return qi::check_launch("attention_prefill_tcgen05");
+}
+
+extern "C" int qi_attention_prefill_tcgen05_ex(const void* q, void* out, const void* k_pages, const void* v_pages,
+                                               const int* block_table, int max_blocks, int page_size, int num_pages,
+                                               const int* q_start, const int* start_pos, const int* tile_req,
+                                               const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int d,
+                                               float scale, int window, int chunk, const void* gate, long long ldg,
+                                               int n_ranges, float* workspace, int* status, float softcap, float out_scale,
+                                               cudaStream_t stream) {
+    return qi_attention_prefill_tcgen05_sink(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start,
+                                             start_pos, tile_req, tile_q0, n_tiles, n_tokens, nq, nkv, d, scale, window, chunk,
+                                             gate, ldg, n_ranges, workspace, status, softcap, out_scale, nullptr, stream);
 }
 
 extern "C" int qi_attention_prefill_tcgen05(const void* q, void* out, const void* k_pages, const void* v_pages,

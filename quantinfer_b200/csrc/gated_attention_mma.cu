@@ -72,7 +72,8 @@ gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict_
                            const qi::bf16* __restrict__ v_pages, const int* __restrict__ block_table, int max_blocks,
                            int page_size, int num_pages, const int* __restrict__ q_start, const int* __restrict__ start_pos,
                            int n_entries, int nq, int nkv, int d, int dv, float scale_log2e, float softcap, float out_scale,
-                           int window, int chunk, const qi::bf16* __restrict__ gate, long long ldg, int* __restrict__ status) {
+                           int window, int chunk, const qi::bf16* __restrict__ gate, long long ldg, const float* __restrict__ sink,
+                           int* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     constexpr int SK = DK + kPad, SV = DV + kPad;
     qi::bf16* Qs = reinterpret_cast<qi::bf16*>(smem_raw);       // [kQT][SK]
@@ -232,6 +233,11 @@ gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict_
     if (bad_page && status) atomicOr(status, qi::kStatusBadPage);
     lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
     lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    if (sink) {       // one more term in the denominator, exp(sink_h), with no key and no value (m is a base-2 exponent)
+        const float sb = sink[h] * 1.4426950408889634f;
+        if (mA != -INFINITY) lA += exp2f(sb - mA);
+        if (mB != -INFINITY) lB += exp2f(sb - mB);
+    }
     const float iA = lA > 0.f ? 1.0f / lA : 0.f, iB = lB > 0.f ? 1.0f / lB : 0.f;   // out_scale joins below, after the gate
 #pragma unroll
     for (int n = 0; n < DV / 8; ++n) {
@@ -259,7 +265,7 @@ template <int DK, int DV>
 int launch_one(dim3 grid, cudaStream_t stream, const void* q, void* out, const void* k_pages, const void* v_pages,
                const int* block_table, int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
                int n_entries, int nq, int nkv, int d, int dv, float scale_log2e, float softcap, float out_scale, int window, int chunk,
-               const void* gate, long long ldg, int* status) {
+               const void* gate, long long ldg, const float* sink, int* status) {
     const size_t smem = sizeof(qi::bf16) * ((size_t)(kQT + 2 * kKT) * (DK + kPad) + (size_t)2 * kKT * (DV + kPad));
     static bool raised = false;
     if (!raised && smem > 48 * 1024) {
@@ -268,7 +274,7 @@ int launch_one(dim3 grid, cudaStream_t stream, const void* q, void* out, const v
     }
     qi::launch(gated_attention_mma_kernel<DK, DV>, grid, dim3(kThreads), smem, stream, (const qi::bf16*)q, (qi::bf16*)out,
                (const qi::bf16*)k_pages, (const qi::bf16*)v_pages, block_table, max_blocks, page_size, num_pages, q_start, start_pos,
-               n_entries, nq, nkv, d, dv, scale_log2e, softcap, out_scale, window, chunk, (const qi::bf16*)gate, ldg, status);
+               n_entries, nq, nkv, d, dv, scale_log2e, softcap, out_scale, window, chunk, (const qi::bf16*)gate, ldg, sink, status);
     return qi::check_launch("gated_attention_mma");
 }
 
@@ -280,11 +286,13 @@ extern "C" int qi_gated_attention_mma_supported(int nq, int nkv, int d, int dv) 
 
 // q [n, nq d], out [n, nq dv], pages [num_pages, nkv, page_size, d | dv], all bfloat16; q_start [entries + 1],
 // start_pos [entries]; gate (may be null) row t, head h, element i at gate[t * ldg + h * dv + i] (ldg and dv even);
-// softcap c > 0: a score s becomes c tanh(s / c) before the softmax; out_scale multiplies the result.
-extern "C" int qi_gated_attention_mma(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
+// softcap c > 0: a score s becomes c tanh(s / c) before the softmax; out_scale multiplies the result. sink (may be null):
+// float32 [nq]; the softmax's denominator of head h holds exp(sink[h]) once more.
+extern "C" int qi_gated_attention_mma_sink(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
                                       int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
                                       int n_entries, int n_tokens, int nq, int nkv, int d, int dv, float scale, float softcap,
-                                      float out_scale, int window, int chunk, const void* gate, long long ldg, int* status, cudaStream_t stream) {
+                                      float out_scale, int window, int chunk, const void* gate, long long ldg, const float* sink,
+                                      int* status, cudaStream_t stream) {
     QI_REQUIRE(qi_gated_attention_mma_supported(nq, nkv, d, dv), "gated_attention_mma: heads %d/%d of %d/%d are not covered", nq, nkv, d, dv);
     QI_REQUIRE(n_entries >= 0 && n_tokens >= 0 && page_size > 0 && max_blocks > 0 && num_pages > 0, "gated_attention_mma: bad sizes");
     QI_REQUIRE(window >= 0 && chunk >= 0, "gated_attention_mma: window and chunk must be >= 0 (0 = none)");
@@ -296,7 +304,7 @@ extern "C" int qi_gated_attention_mma(const void* q, void* out, const void* k_pa
     const float sl = scale * 1.4426950408889634f;
 #define QI_GA(DKP, DVP)                                                                                                      \
     return launch_one<DKP, DVP>(grid, stream, q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start, \
-                                start_pos, n_entries, nq, nkv, d, dv, sl, softcap, out_scale, window, chunk, gate, ldg, status)
+                                start_pos, n_entries, nq, nkv, d, dv, sl, softcap, out_scale, window, chunk, gate, ldg, sink, status)
 #define QI_GA_ROW(DKP)                                   \
     switch (padded(dv)) {                                \
         case 32: QI_GA(DKP, 32);                         \
@@ -313,4 +321,13 @@ extern "C" int qi_gated_attention_mma(const void* q, void* out, const void* k_pa
 #undef QI_GA_ROW
 #undef QI_GA
     return 0;
+}
+
+extern "C" int qi_gated_attention_mma(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
+                                      int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
+                                      int n_entries, int n_tokens, int nq, int nkv, int d, int dv, float scale, float softcap,
+                                      float out_scale, int window, int chunk, const void* gate, long long ldg, int* status, cudaStream_t stream) {
+    return qi_gated_attention_mma_sink(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start, start_pos,
+                                       n_entries, n_tokens, nq, nkv, d, dv, scale, softcap, out_scale, window, chunk, gate, ldg, nullptr,
+                                       status, stream);
 }

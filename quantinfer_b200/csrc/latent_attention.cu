@@ -17,8 +17,9 @@
 // qi_latent_prepare: per token, from the row of the fused projection [q heads | latent projection]:
 // rotates each head's r-part into the query buffer, and (when the layer projects its own latent)
 // normalises the latent (32-bit, gain per coordinate), rotates the shared key part and writes the row
-// into the paged cache. Rotation: pair (2i, 2i + 1) of the first `rot_dims` coordinates of the part turns by
-// the angle position * inv_freq[i], computed here in 32-bit (no table, so no limit on positions).
+// into the paged cache. Rotation: pair i of the first `rot_dims` coordinates of the part, (2i, 2i + 1) or, when
+// `half_split`, (i, i + rot_dims / 2), turns by the angle position * inv_freq[i], computed here in 32-bit (no
+// table, so no limit on positions); cos and sin are multiplied by `magnitude` (1 for the plain rotation).
 //
 // qi_latent_attention_generic: 32-bit arithmetic for any sizes; one block per (token, head).
 #include "common.cuh"
@@ -33,7 +34,8 @@ latent_prepare_kernel(const TP* __restrict__ proj, long long ldp, int kv_off, T*
                       const float* __restrict__ gain, float eps, const float* __restrict__ inv_freq, int rot_dims,
                       const int* __restrict__ positions, const int* __restrict__ token_req,
                       const int* __restrict__ block_table, int max_blocks, int page_size, int num_pages,
-                      T* __restrict__ cache, int H, int d, int r, int R, int* __restrict__ status) {
+                      T* __restrict__ cache, int H, int d, int r, int R, int half_split, float magnitude,
+                      int* __restrict__ status) {
     extern __shared__ float smem[];
     float* cs = smem;                 // [rot_dims / 2]
     float* sn = smem + rot_dims / 2;  // [rot_dims / 2]
@@ -45,8 +47,8 @@ latent_prepare_kernel(const TP* __restrict__ proj, long long ldp, int kv_off, T*
         const float a = (float)pos * inv_freq[i];
         float s, c;
         sincosf(a, &s, &c);
-        cs[i] = c;
-        sn[i] = s;
+        cs[i] = c * magnitude;
+        sn[i] = s * magnitude;
     }
     __syncthreads();
     const TP* row = proj + (size_t)t * ldp;
@@ -57,9 +59,11 @@ latent_prepare_kernel(const TP* __restrict__ proj, long long ldp, int kv_off, T*
         const TP* part = row + (size_t)h * (d + r) + d;
         float v;
         if (j < rot_dims) {
-            const int i = j >> 1;
-            const float a = qi::to_f32<TP>(part[2 * i]), b = qi::to_f32<TP>(part[2 * i + 1]);
-            v = (j & 1) ? b * cs[i] + a * sn[i] : a * cs[i] - b * sn[i];
+            const int half = rot_dims >> 1;
+            const int i = half_split ? (j < half ? j : j - half) : j >> 1;
+            const bool second = half_split ? j >= half : (j & 1);
+            const float a = qi::to_f32<TP>(part[half_split ? i : 2 * i]), b = qi::to_f32<TP>(part[half_split ? i + half : 2 * i + 1]);
+            v = second ? b * cs[i] + a * sn[i] : a * cs[i] - b * sn[i];
         } else {
             v = qi::to_f32<TP>(part[j]);
         }
@@ -84,9 +88,11 @@ latent_prepare_kernel(const TP* __restrict__ proj, long long ldp, int kv_off, T*
     for (int j = threadIdx.x; j < r; j += blockDim.x) {
         float v;
         if (j < rot_dims) {
-            const int i = j >> 1;
-            const float a = qi::to_f32<TP>(z[R + 2 * i]), b = qi::to_f32<TP>(z[R + 2 * i + 1]);
-            v = (j & 1) ? b * cs[i] + a * sn[i] : a * cs[i] - b * sn[i];
+            const int half = rot_dims >> 1;
+            const int i = half_split ? (j < half ? j : j - half) : j >> 1;
+            const bool second = half_split ? j >= half : (j & 1);
+            const float a = qi::to_f32<TP>(z[R + (half_split ? i : 2 * i)]), b = qi::to_f32<TP>(z[R + (half_split ? i + half : 2 * i + 1)]);
+            v = second ? b * cs[i] + a * sn[i] : a * cs[i] - b * sn[i];
         } else {
             v = qi::to_f32<TP>(z[R + j]);
         }
@@ -204,7 +210,7 @@ extern "C" int qi_latent_prepare(const void* proj, int proj_dtype, long long ldp
                                  const float* gain, float eps, const float* inv_freq, int rot_dims,
                                  const int* positions, const int* token_req, const int* block_table, int max_blocks,
                                  int page_size, int num_pages, void* cache, int n_tokens, int H, int d, int r, int R,
-                                 int* status, cudaStream_t stream) {
+                                 int half_split, float magnitude, int* status, cudaStream_t stream) {
     QI_REQUIRE(n_tokens >= 0 && H > 0 && d > 0 && r >= 0 && R > 0, "latent_prepare: bad sizes");
     QI_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= r, "latent_prepare: %d rotated coordinates do not fit a part of %d", rot_dims, r);
     QI_REQUIRE(rot_dims == 0 || inv_freq, "latent_prepare: the rotation's frequencies are missing");
@@ -219,7 +225,7 @@ extern "C" int qi_latent_prepare(const void* proj, int proj_dtype, long long ldp
         QI_DISPATCH_DTYPE(dtype, T, {
             qi::launch(latent_prepare_kernel<TP, T>, dim3(n_tokens), dim3(128), smem, stream, (const TP*)proj, ldp, kv_off, (T*)q_out, gain,
                        eps, inv_freq, rot_dims, positions, token_req, block_table, max_blocks, page_size, num_pages, (T*)cache,
-                       H, d, r, R, status);
+                       H, d, r, R, half_split, magnitude, status);
         });
     });
     return qi::check_launch("latent_prepare");

@@ -487,4 +487,186 @@ extern "C" int qi_rmsnorm(const void* x, const float* gain, float eps, void* out
     return qi::check_launch("rmsnorm");
 }
 
+
+// ---- norms that come after the sum ------------------------------------------------------------------
+//
+// For every row:  x = alpha * resid + sum_k delta[k]   (32-bit, k ascending; delta may be null)
+//                 y = x / sqrt(mean(x^2) + eps) * gain
+//                 resid = y (32-bit)   and, when `copy` is given, copy = y in its type
+// The stream itself is normalised, so the next sublayer reads `resid` (or its copy in the activation type) as it is.
+namespace {
+
+template <typename TD, typename TO>
+__global__ void scale_add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, int delta_splits,
+                                         size_t delta_split_stride, float alpha, const float* __restrict__ gain, float eps,
+                                         TO* __restrict__ copy, int hidden) {
+    __shared__ float scratch[32];
+    qi::pdl_wait();
+    const int r = blockIdx.x;
+    float* xr = resid + (size_t)r * hidden;
+    const TD* dr = delta ? delta + (size_t)r * hidden : nullptr;
+    float sumsq = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float x = alpha * xr[i];
+        if (dr) {
+            float d = qi::to_f32<TD>(dr[i]);
+            for (int k = 1; k < delta_splits; ++k) d += qi::to_f32<TD>(dr[k * delta_split_stride + i]);
+            x += d;
+        }
+        xr[i] = x;                       // the same thread reads it again below
+        sumsq = fmaf(x, x, sumsq);
+    }
+    const float inv = 1.0f / sqrtf(qi::block_sum(sumsq, scratch) / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float y = xr[i] * inv * gain[i];
+        xr[i] = y;
+        if (copy) copy[(size_t)r * hidden + i] = qi::from_f32<TO>(y);
+    }
+}
+
+// The same with a row in registers: eight neighbouring coordinates a thread (rows of up to 8 x blockDim), every
+// operand read once; a CTA takes rows blockIdx.x, blockIdx.x + gridDim.x, ...
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(512, 3) scale_add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                             int delta_splits, size_t delta_split_stride, float alpha,
+                                             const float* __restrict__ gain, float eps, TO* __restrict__ copy, int hidden,
+                                             int n_rows) {
+    __shared__ float scratch[32];
+    qi::pdl_wait();
+    const int i = threadIdx.x * 8;
+    const bool active = i < hidden;
+    for (int r = blockIdx.x; r < n_rows; r += gridDim.x) {
+        float* xr = resid + (size_t)r * hidden;
+        const TD* dr = delta ? delta + (size_t)r * hidden : nullptr;
+        float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, d[8], g[8], acc[8];
+        if (active) {
+            Vec8<float>::load(xr + i, x);
+            Vec8<float>::load(gain + i, g);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] *= alpha;
+            if (dr) {
+                Vec8<TD>::load(dr + i, acc);
+#pragma unroll 4
+                for (int k = 1; k < delta_splits; ++k) {
+                    Vec8<TD>::load(dr + k * delta_split_stride + i, d);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] += d[j];
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[j] += acc[j];
+            }
+        }
+        float sumsq = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sumsq = fmaf(x[j], x[j], sumsq);
+        const float inv = 1.0f / sqrtf(qi::block_sum(sumsq, scratch) / (float)hidden + eps);
+        if (active) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = x[j] * inv * g[j];
+            Vec8<float>::store(xr + i, x);
+            if (copy) Vec8<TO>::store(copy + (size_t)r * hidden + i, x);
+        }
+    }
+}
+
+// out = s * (a / rms(a) * ga + b / rms(b) * gb), a and b each whole or as the partial sums of a split product.
+template <typename TA, typename TB>
+__global__ void normed_sum_kernel(const TA* __restrict__ a, int ka, const TB* __restrict__ b, int kb, size_t part_stride,
+                                  const float* __restrict__ ga, const float* __restrict__ gb, float eps, float s,
+                                  float* __restrict__ out, int hidden) {
+    __shared__ float scratch[32];
+    qi::pdl_wait();
+    const size_t row = (size_t)blockIdx.x * hidden;
+    auto va = [&](int i) {
+        float x = qi::to_f32<TA>(a[row + i]);
+        for (int k = 1; k < ka; ++k) x += qi::to_f32<TA>(a[k * part_stride + row + i]);
+        return x;
+    };
+    auto vb = [&](int i) {
+        float x = qi::to_f32<TB>(b[row + i]);
+        for (int k = 1; k < kb; ++k) x += qi::to_f32<TB>(b[k * part_stride + row + i]);
+        return x;
+    };
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float x = va(i), y = vb(i);
+        sa = fmaf(x, x, sa);
+        sb = fmaf(y, y, sb);
+    }
+    const float ia = 1.0f / sqrtf(qi::block_sum(sa, scratch) / (float)hidden + eps);
+    const float ib = 1.0f / sqrtf(qi::block_sum(sb, scratch) / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        out[row + i] = s * (va(i) * ia * ga[i] + vb(i) * ib * gb[i]);
+}
+
+template <typename TO>
+__global__ void convert_kernel(const float* __restrict__ x, TO* __restrict__ out, size_t n) {
+    qi::pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = qi::from_f32<TO>(x[i]);
+}
+
+}  // namespace
+
+// resid float32 [n_rows, hidden], updated in place; delta (or null) [splits, n_rows, hidden]; copy (or null) receives the
+// new rows in `copy_dtype`.
+extern "C" int qi_scale_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int delta_splits, long long delta_split_stride,
+                                    float alpha, const float* gain, float eps, void* copy, int copy_dtype, int n_rows, int hidden,
+                                    cudaStream_t stream) {
+    QI_REQUIRE(n_rows >= 0 && hidden > 0 && delta_splits >= 1, "scale_add_rmsnorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
+    QI_REQUIRE(eps > 0.f, "scale_add_rmsnorm: eps must be positive");
+    if (n_rows == 0) return 0;
+    const int dd = delta ? delta_dtype : qi::kF32;
+    const int cd = copy ? copy_dtype : qi::kF32;
+    const bool vec = hidden % 8 == 0 && hidden <= 4096 && ((uintptr_t)resid & 31) == 0 && ((uintptr_t)delta & 15) == 0 &&
+                     ((uintptr_t)copy & 15) == 0 && ((uintptr_t)gain & 15) == 0 && delta_split_stride % 8 == 0;
+    if (vec) {
+        const int threads = (hidden / 8 + 31) / 32 * 32;
+        const int resident = 148 * (2048 / threads < 3 ? 2048 / threads : 3) * (threads < 512 ? 512 / threads : 1);
+        const int grid = n_rows < resident ? n_rows : resident;
+        QI_DISPATCH_DTYPE(dd, TD, {
+            QI_DISPATCH_DTYPE(cd, TO, {
+                qi::launch(scale_add_rmsnorm_vec_kernel<TD, TO>, dim3(grid), dim3(threads), 0, stream, resid, (const TD*)delta,
+                           delta_splits, (size_t)delta_split_stride, alpha, gain, eps, (TO*)copy, hidden, n_rows);
+            });
+        });
+        return qi::check_launch("scale_add_rmsnorm");
+    }
+    const int threads = pick_threads(hidden);
+    QI_DISPATCH_DTYPE(dd, TD, {
+        QI_DISPATCH_DTYPE(cd, TO, {
+            qi::launch(scale_add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream, resid, (const TD*)delta,
+                       delta_splits, (size_t)delta_split_stride, alpha, gain, eps, (TO*)copy, hidden);
+        });
+    });
+    return qi::check_launch("scale_add_rmsnorm");
+}
+
+// a [ka, n_rows, hidden] in `dtype_a`, b [kb, n_rows, hidden] in `dtype_b`; ga, gb float32 [hidden]; out float32.
+extern "C" int qi_normed_sum(const void* a, int ka, int dtype_a, const void* b, int kb, int dtype_b, const float* ga,
+                             const float* gb, float eps, float scale, float* out, int n_rows, int hidden, cudaStream_t stream) {
+    QI_REQUIRE(n_rows >= 0 && hidden > 0 && ka >= 1 && kb >= 1 && eps > 0.f, "normed_sum: bad sizes");
+    if (n_rows == 0) return 0;
+    const int threads = pick_threads(hidden);
+    QI_DISPATCH_DTYPE(dtype_a, TA, {
+        QI_DISPATCH_DTYPE(dtype_b, TB, {
+            qi::launch(normed_sum_kernel<TA, TB>, dim3(n_rows), dim3(threads), 0, stream, (const TA*)a, ka, (const TB*)b, kb,
+                       (size_t)n_rows * hidden, ga, gb, eps, scale, out, hidden);
+        });
+    });
+    return qi::check_launch("normed_sum");
+}
+
+// out[i] = x[i] in `out_dtype`; x float32.
+extern "C" int qi_convert(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    QI_REQUIRE(n >= 0, "convert: bad size");
+    if (n == 0) return 0;
+    size_t blocks = ((size_t)n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    QI_DISPATCH_DTYPE(out_dtype, TO, {
+        qi::launch(convert_kernel<TO>, dim3((unsigned)blocks), dim3(256), 0, stream, x, (TO*)out, (size_t)n);
+    });
+    return qi::check_launch("convert");
+}
+
 QI_TL_EXPORT(qi_timeline_norm)

@@ -300,6 +300,8 @@ extern "C" int qi_qk_norm_rope_kv(const void* qkv, int qkv_splits, void* q_out, 
 // head turn by angle = position * inv_freq[pair] (32-bit product, sincosf), pairs (i, i + rot / 2) or, when
 // `interleaved`, (2i, 2i + 1); q goes to q_out [n, nq d], k and v into the request's pages
 // (k_pages [pages, nkv, page_size, d], v_pages [pages, nkv, page_size, dv]; null: nothing is written).
+// Two options for designs that ask for them: one RMS norm over the whole of q and one over the whole of k (all heads
+// at once, gain per coordinate) before the rotation; and values that are the keys as projected (no v in the row).
 namespace {
 
 template <typename T>
@@ -308,7 +310,9 @@ bias_rope_kv_kernel(const T* __restrict__ proj, long long ld, const float* __res
                     const float* __restrict__ inv_freq, int rot, int interleaved, const int* __restrict__ positions,
                     const int* __restrict__ token_req, const int* __restrict__ block_table, int max_blocks, int page_size,
                     int num_pages, T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv, int d, int dv,
+                    const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps, int v_from_k,
                     int* __restrict__ status) {
+    __shared__ float scratch[32];
     qi::pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
@@ -317,7 +321,23 @@ bias_rope_kv_kernel(const T* __restrict__ proj, long long ld, const float* __res
         return;
     }
     const T* row = proj + (size_t)t * ld;
-    const int qk = (nq + nkv) * d, total = qk + nkv * dv;
+    const int qk = (nq + nkv) * d, total = v_from_k ? qk : qk + nkv * dv;
+    // one RMS norm over all of q and one over all of k (before the rotation), when their gains are given
+    float q_inv = 1.f, k_inv = 1.f;
+    if (q_gain) {
+        float sq = 0.f, sk = 0.f;
+        for (int e = threadIdx.x; e < qk; e += blockDim.x) {
+            const float x = qi::to_f32<T>(row[e]) + (bias ? bias[e] : 0.f);
+            if (e < nq * d) sq = fmaf(x, x, sq); else sk = fmaf(x, x, sk);
+        }
+        q_inv = 1.0f / sqrtf(qi::block_sum(sq, scratch) / (float)(nq * d) + eps);
+        k_inv = 1.0f / sqrtf(qi::block_sum(sk, scratch) / (float)(nkv * d) + eps);
+    }
+    auto normed = [&](int e) {
+        float x = qi::to_f32<T>(row[e]) + (bias ? bias[e] : 0.f);
+        if (q_gain) x = e < nq * d ? x * q_inv * q_gain[e] : x * k_inv * k_gain[e - nq * d];
+        return x;
+    };
     T* krow = nullptr;
     T* vrow = nullptr;
     if (k_pages) {
@@ -338,13 +358,15 @@ bias_rope_kv_kernel(const T* __restrict__ proj, long long ld, const float* __res
             continue;
         }
         const int head = e / d, i = e % d;
-        float x = qi::to_f32<T>(row[e]) + (bias ? bias[e] : 0.f);
+        float x = normed(e);
+        if (v_from_k && head >= nq && vrow)     // the value is the key as projected, before norm and rotation
+            vrow[(size_t)(head - nq) * page_size * dv + i] = qi::from_f32<T>(qi::to_f32<T>(row[e]) + (bias ? bias[e] : 0.f));
         if (i < rot) {
             int pair, other;
             bool first;
             if (interleaved) { pair = i >> 1; first = !(i & 1); other = first ? e + 1 : e - 1; }
             else { first = i < half; pair = first ? i : i - half; other = first ? e + half : e - half; }
-            const float o = qi::to_f32<T>(row[other]) + (bias ? bias[other] : 0.f);
+            const float o = normed(other);
             float sn, cs;
             sincosf((float)pos * inv_freq[pair], &sn, &cs);
             x = first ? x * cs - o * sn : x * cs + o * sn;
@@ -356,22 +378,36 @@ bias_rope_kv_kernel(const T* __restrict__ proj, long long ld, const float* __res
 
 }  // namespace
 
-extern "C" int qi_bias_rope_kv(const void* proj, long long ld, const float* bias, void* q_out, int dtype,
+// q_gain, k_gain (both or neither; float32 [nq d], [nkv d]): q as a whole and k as a whole each pass an RMS norm with that
+// gain and `eps` before the rotation. v_from_k: the rows hold no v; a position's value is its key as projected (dv = d).
+extern "C" int qi_norm_rope_kv(const void* proj, long long ld, const float* bias, void* q_out, int dtype,
                                const float* inv_freq, int rot, int interleaved, const int* positions,
                                const int* token_req, const int* block_table, int max_blocks, int page_size,
                                int num_pages, void* k_pages, void* v_pages, int n_tokens, int nq, int nkv, int d,
-                               int dv, int* status, cudaStream_t stream) {
+                               int dv, const float* q_gain, const float* k_gain, float eps, int v_from_k, int* status,
+                               cudaStream_t stream) {
     QI_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0 && dv > 0, "bias_rope_kv: bad sizes");
     QI_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= d, "bias_rope_kv: %d rotated coordinates do not fit a head of %d", rot, d);
     QI_REQUIRE(rot == 0 || inv_freq, "bias_rope_kv: a rotation needs its inverse frequencies");
-    QI_REQUIRE(ld >= (long long)(nq + nkv) * d + (long long)nkv * dv, "bias_rope_kv: the rows are too short");
+    QI_REQUIRE((q_gain == nullptr) == (k_gain == nullptr) && (!q_gain || eps > 0.f), "bias_rope_kv: the norms of q and k come together, with a positive eps");
+    QI_REQUIRE(!v_from_k || dv == d, "bias_rope_kv: values that are the keys have the keys' size");
+    QI_REQUIRE(ld >= (long long)(nq + nkv) * d + (v_from_k ? 0 : (long long)nkv * dv), "bias_rope_kv: the rows are too short");
     QI_REQUIRE((k_pages == nullptr) == (v_pages == nullptr), "bias_rope_kv: key and value pages come together");
     QI_REQUIRE(!k_pages || (block_table && max_blocks > 0 && page_size > 0 && num_pages > 0), "bias_rope_kv: bad page geometry");
     if (n_tokens == 0) return 0;
     QI_DISPATCH_DTYPE(dtype, T, {
         qi::launch(bias_rope_kv_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)proj, ld, bias, (T*)q_out, inv_freq, rot,
                    interleaved, positions, token_req, block_table, max_blocks, page_size, num_pages, (T*)k_pages, (T*)v_pages,
-                   nq, nkv, d, dv, status);
+                   nq, nkv, d, dv, q_gain, k_gain, eps, v_from_k, status);
     });
     return qi::check_launch("bias_rope_kv");
+}
+
+extern "C" int qi_bias_rope_kv(const void* proj, long long ld, const float* bias, void* q_out, int dtype,
+                               const float* inv_freq, int rot, int interleaved, const int* positions,
+                               const int* token_req, const int* block_table, int max_blocks, int page_size,
+                               int num_pages, void* k_pages, void* v_pages, int n_tokens, int nq, int nkv, int d,
+                               int dv, int* status, cudaStream_t stream) {
+    return qi_norm_rope_kv(proj, ld, bias, q_out, dtype, inv_freq, rot, interleaved, positions, token_req, block_table, max_blocks,
+                           page_size, num_pages, k_pages, v_pages, n_tokens, nq, nkv, d, dv, nullptr, nullptr, 0.f, 0, status, stream);
 }

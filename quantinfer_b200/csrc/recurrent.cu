@@ -158,12 +158,16 @@ token_shift_kernel(const T* __restrict__ h, const float* __restrict__ mu, float*
 //   mode 0 (decay per key channel, bonus):   o_t = S_(t-1)^T r_t + (sum_i r_i u_i k_i) v_t ;  S_t = diag(w_t) S_(t-1) + k_t v_t^T
 //                                            w_t = exp(-exp(lw_t + w0)) from the decay projection's output lw
 //   mode 1 (one decay a head, silu inputs):  S_t = lambda S_(t-1) + k_t v_t^T ;  o_t = S_t^T q_t ;  q, k, v = silu of the projections
+//   mode 2 (gated delta rule):               S' = diag(w_t) S_(t-1) ;  u_t = beta_t (v_t - S'^T k_t) ;  S_t = S' + k_t u_t^T ;  o_t = S_t^T q_t
+//                                            q, k unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q times q_scale; beta_t = sigmoid(b_t);
+//                                            w_t = exp(-exp(A_h) softplus(lw_t + w0)); heads / qk_heads value heads share a q/k head.
+//                                            Every column of S moves on its own, so the thread that keeps it needs no other.
 // A block owns one entry, one head and up to kColThreads value columns; thread j keeps column j of S in registers
 // (DK numbers, dk padded with zeros). The operands of kStage tokens are staged in shared memory at a time (decays and
 // activations are evaluated there, once a token and channel: thread x stages key channels x, x + kColThreads, ...); in
 // the inner loop every thread reads them as broadcasts. The state of a slot is laid out [heads, dv, dk], dk fastest.
 //
-// The recurrence is linear in S, so long entries are cut into segments that run side by side, as three launches:
+// Modes 0 and 1 are linear in S with a diagonal factor, so long entries are cut into segments that run side by side, as three launches:
 // every segment as an entry of its own from zeros, without outputs (o null), leaving its own contribution in a
 // scratch row and the product of its decays per key channel in `decay_out`; matrix_state_chain_kernel, which walks an
 // entry's segments in order, replaces each contribution by the state its segment starts from and moves the request's
@@ -178,15 +182,18 @@ matrix_state_scan_kernel(const T* __restrict__ r, long long ldr, const T* __rest
                          const float* __restrict__ u, const float* __restrict__ lambda, float* __restrict__ state,
                          long long state_stride, float* __restrict__ o, float* __restrict__ decay_out, int write_state,
                          const int* __restrict__ q_start, const int* __restrict__ start_pos, const int* __restrict__ slot_ids,
-                         int heads, int dk, int dv) {
+                         int heads, int dk, int dv, const T* __restrict__ bproj, long long ldb, int qk_heads, float unit_eps,
+                         float q_scale) {
     constexpr int kOwn = (DK + kColThreads - 1) / kColThreads;     // key channels a thread stages
     static_assert(DK % 4 == 0, "the staged operands are read four at a time");
     constexpr int kStage = DK <= 64 ? 8 : 4;                       // tokens a stage
     constexpr int kBonusLanes = kColThreads / kStage;              // threads that share a token's bonus sum
     __shared__ __align__(16) float s_r[kStage][DK], s_k[kStage][DK], s_w[kStage][DK];
     __shared__ float s_v[kStage][kColThreads], s_bonus[kStage], s_u[MODE == 0 ? DK : 1];
+    __shared__ float s_qs[kStage], s_ks[kStage], s_beta[kStage];      // mode 2: the factors that make q and k unit vectors, and beta
     qi::pdl_wait();
     const int hd = blockIdx.x, e = blockIdx.y;
+    const int hq = MODE == 2 ? hd / (heads / qk_heads) : hd;          // the head of r and k that this head reads
     const int j = blockIdx.z * kColThreads + threadIdx.x;
     const bool live = j < dv;
     const int first = q_start[e], len = q_start[e + 1] - first;
@@ -209,19 +216,19 @@ matrix_state_scan_kernel(const T* __restrict__ r, long long ldr, const T* __rest
             for (int i = 0; i < DK; ++i) if (i < dk) S[i] = st[i];
         }
     }
-    const float lam = MODE == 1 ? lambda[hd] : 0.f;
+    const float lam = MODE == 1 ? lambda[hd] : MODE == 2 ? expf(lambda[hd]) : 0.f;
     float w0r[kOwn], dsum[kOwn];        // dsum: minus the logarithm of the product of this entry's decays
 #pragma unroll
     for (int m = 0; m < kOwn; ++m) {
         const int i = threadIdx.x + m * kColThreads;
-        const bool in = MODE == 0 && i < dk;
+        const bool in = MODE != 1 && i < dk;
         w0r[m] = in ? w0[(size_t)hd * dk + i] : 0.f;
         dsum[m] = 0.f;
     }
     if (MODE == 0)
         for (int i = threadIdx.x; i < DK; i += kColThreads) s_u[i] = i < dk ? u[(size_t)hd * dk + i] : 0.f;
     // A stage's numbers are fetched into registers one stage ahead, while the stage before is worked through.
-    T f_r[kOwn][kStage], f_k[kOwn][kStage], f_w[MODE == 0 ? kOwn : 1][kStage], f_v[kStage];
+    T f_r[kOwn][kStage], f_k[kOwn][kStage], f_w[MODE != 1 ? kOwn : 1][kStage], f_v[kStage], f_b = qi::from_f32<T>(0.f);
     auto fetch = [&](int base) {
         const int nt = min(kStage, len - base);
 #pragma unroll
@@ -232,15 +239,16 @@ matrix_state_scan_kernel(const T* __restrict__ r, long long ldr, const T* __rest
             for (int tt = 0; tt < kStage; ++tt) {
                 if (in && tt < nt) {
                     const size_t row = (size_t)(first + base + tt);
-                    f_r[m][tt] = r[row * ldr + (size_t)hd * dk + i];
-                    f_k[m][tt] = k[row * ldk + (size_t)hd * dk + i];
-                    if (MODE == 0) f_w[m][tt] = lw[row * ldw + (size_t)hd * dk + i];
+                    f_r[m][tt] = r[row * ldr + (size_t)hq * dk + i];
+                    f_k[m][tt] = k[row * ldk + (size_t)hq * dk + i];
+                    if (MODE != 1) f_w[m][tt] = lw[row * ldw + (size_t)hd * dk + i];
                 }
             }
         }
 #pragma unroll
         for (int tt = 0; tt < kStage; ++tt)
             if (live && tt < nt) f_v[tt] = v[(size_t)(first + base + tt) * ldv + (size_t)hd * dv + j];
+        if (MODE == 2 && (int)threadIdx.x < nt) f_b = bproj[(size_t)(first + base + threadIdx.x) * ldb + hd];
     };
     if (len > 0) fetch(0);
     for (int base = 0; base < len; base += kStage) {
@@ -262,14 +270,17 @@ matrix_state_scan_kernel(const T* __restrict__ r, long long ldr, const T* __rest
                                 const float rate = expf(qi::to_f32<T>(f_w[m][tt]) + w0r[m]);
                                 wv = expf(-rate);
                                 dsum[m] += rate;
-                            } else {
+                            } else if (MODE == 1) {
                                 rv = siluf_(rv);
                                 kv = siluf_(kv);
+                            } else {
+                                const float x = qi::to_f32<T>(f_w[m][tt]) + w0r[m];
+                                wv = expf(-lam * (x > 20.f ? x : log1pf(expf(x))));      // softplus
                             }
                         }
                         s_r[tt][i] = rv;
                         s_k[tt][i] = kv;
-                        if (MODE == 0) s_w[tt][i] = wv;
+                        if (MODE != 1) s_w[tt][i] = wv;
                     }
                 }
             }
@@ -282,7 +293,28 @@ matrix_state_scan_kernel(const T* __restrict__ r, long long ldr, const T* __rest
                 s_v[tt][threadIdx.x] = vv;
             }
         }
+        if (MODE == 2 && (int)threadIdx.x < nt) s_beta[threadIdx.x] = 1.0f / (1.0f + expf(-qi::to_f32<T>(f_b)));
         if (base + kStage < len) fetch(base + kStage);
+        if (MODE == 2) {
+            __syncthreads();
+            // the lengths of a token's q and k: kBonusLanes threads a token, each every kBonusLanes-th channel
+            const int tt = threadIdx.x / kBonusLanes, sub = threadIdx.x % kBonusLanes;
+            float sq = 0.f, sk = 0.f;
+            if (tt < nt)
+                for (int i = sub; i < DK; i += kBonusLanes) {
+                    sq = fmaf(s_r[tt][i], s_r[tt][i], sq);
+                    sk = fmaf(s_k[tt][i], s_k[tt][i], sk);
+                }
+#pragma unroll
+            for (int d = kBonusLanes / 2; d > 0; d >>= 1) {
+                sq += __shfl_xor_sync(0xffffffffu, sq, d);
+                sk += __shfl_xor_sync(0xffffffffu, sk, d);
+            }
+            if (sub == 0 && tt < nt) {
+                s_qs[tt] = q_scale / sqrtf(sq + unit_eps);
+                s_ks[tt] = 1.0f / sqrtf(sk + unit_eps);
+            }
+        }
         if (MODE == 0 && o) {
             __syncthreads();
             // the bonus of the current token, sum_i r_i u_i k_i: kBonusLanes threads a token, each every kBonusLanes-th channel
@@ -296,6 +328,45 @@ matrix_state_scan_kernel(const T* __restrict__ r, long long ldr, const T* __rest
         }
         __syncthreads();
         // every thread reads the staged operands as broadcasts, four key channels an instruction
+        if (MODE == 2) {
+            for (int tt = 0; tt < nt; ++tt) {
+                const float vj = s_v[tt][threadIdx.x], ks = s_ks[tt];
+                const float4* r4 = reinterpret_cast<const float4*>(s_r[tt]);
+                const float4* k4 = reinterpret_cast<const float4*>(s_k[tt]);
+                const float4* w4 = reinterpret_cast<const float4*>(s_w[tt]);
+                float p4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < DK; i += 4) {           // the decay, and what the decayed state holds for this key
+                    const float4 kk = k4[i >> 2], ww = w4[i >> 2];
+                    S[i] *= ww.x;
+                    p4[0] = fmaf(kk.x, S[i], p4[0]);
+                    S[i + 1] *= ww.y;
+                    p4[1] = fmaf(kk.y, S[i + 1], p4[1]);
+                    S[i + 2] *= ww.z;
+                    p4[2] = fmaf(kk.z, S[i + 2], p4[2]);
+                    S[i + 3] *= ww.w;
+                    p4[3] = fmaf(kk.w, S[i + 3], p4[3]);
+                }
+                const float held = ((p4[0] + p4[1]) + (p4[2] + p4[3])) * ks;
+                const float uk = s_beta[tt] * (vj - held) * ks;      // the correction, times the factor of the unit key
+                float acc4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < DK; i += 4) {
+                    const float4 rr = r4[i >> 2], kk = k4[i >> 2];
+                    S[i] = fmaf(kk.x, uk, S[i]);
+                    acc4[0] = fmaf(rr.x, S[i], acc4[0]);
+                    S[i + 1] = fmaf(kk.y, uk, S[i + 1]);
+                    acc4[1] = fmaf(rr.y, S[i + 1], acc4[1]);
+                    S[i + 2] = fmaf(kk.z, uk, S[i + 2]);
+                    acc4[2] = fmaf(rr.z, S[i + 2], acc4[2]);
+                    S[i + 3] = fmaf(kk.w, uk, S[i + 3]);
+                    acc4[3] = fmaf(rr.w, S[i + 3], acc4[3]);
+                }
+                if (live && o)
+                    o[(size_t)(first + base + tt) * ((size_t)heads * dv) + (size_t)hd * dv + j] = ((acc4[0] + acc4[1]) + (acc4[2] + acc4[3])) * s_qs[tt];
+            }
+            continue;
+        }
         if (!o) {                       // a segment's own contribution only
             for (int tt = 0; tt < nt; ++tt) {
                 const float vj = s_v[tt][threadIdx.x];
@@ -361,7 +432,7 @@ matrix_state_scan_kernel(const T* __restrict__ r, long long ldr, const T* __rest
             for (int i = 0; i < DK; ++i) if (i < dk) st[i] = S[i];
         }
     }
-    if (decay_out && blockIdx.z == 0) {
+    if (MODE != 2 && decay_out && blockIdx.z == 0) {
         float all = 1.f;
         if (MODE == 1) for (int t = 0; t < len; ++t) all *= lam;
 #pragma unroll
@@ -479,15 +550,24 @@ extern "C" int qi_matrix_state_scan_supported(int dk) { return dk > 0 && dk <= 2
 // state float32 [heads, dv, dk] a slot, `state_stride` floats apart; o float32 [n, heads dv], or null: no outputs
 // (a segment's own contribution is all that is wanted). decay_out (or null): float32 [n_entries, heads, dk], receives
 // the product of each entry's decays per key channel. write_state 0: the state is read, not written.
-extern "C" int qi_matrix_state_scan(int mode, const void* r, long long ldr, const void* k, long long ldk, const void* v, long long ldv,
+// mode 2: r (the queries) and k [n, >= qk_heads dk], v [n, >= heads dv], lw [n, >= heads dk] (the decay projection's
+// output), bproj [n, >= heads] (beta's logits) in `dtype`; w0 float32 [heads dk] (added to lw); lambda float32 [heads] (the
+// logarithm of each head's rate); unit_eps inside the root of the unit vectors; q_scale a factor on the unit query.
+// Mode 2 runs every entry in one piece (decay_out must be null).
+extern "C" int qi_matrix_state_scan_ex(int mode, const void* r, long long ldr, const void* k, long long ldk, const void* v, long long ldv,
                                     const void* lw, long long ldw, int dtype, const float* w0, const float* u, const float* lambda,
                                     float* state, long long state_stride, float* o, float* decay_out, int write_state,
                                     const int* q_start, const int* start_pos, const int* slot_ids, int n_entries, int heads,
-                                    int dk, int dv, cudaStream_t stream) {
-    QI_REQUIRE(mode == 0 || mode == 1, "matrix_state_scan: unknown mode %d", mode);
+                                    int dk, int dv, const void* bproj, long long ldb, int qk_heads, float unit_eps, float q_scale,
+                                    cudaStream_t stream) {
+    QI_REQUIRE(mode >= 0 && mode <= 2, "matrix_state_scan: unknown mode %d", mode);
     QI_REQUIRE(n_entries >= 0 && heads > 0 && dv > 0 && qi_matrix_state_scan_supported(dk), "matrix_state_scan: bad sizes (keys of 1..256)");
-    QI_REQUIRE(ldr >= (long long)heads * dk && ldk >= (long long)heads * dk && ldv >= (long long)heads * dv, "matrix_state_scan: the rows are too short");
-    QI_REQUIRE(mode == 1 || (lw && w0 && u && ldw >= (long long)heads * dk), "matrix_state_scan: the decay's operands are missing");
+    if (mode != 2) qk_heads = heads;
+    QI_REQUIRE(qk_heads > 0 && heads % qk_heads == 0, "matrix_state_scan: %d heads are not a multiple of %d heads of q and k", heads, qk_heads);
+    QI_REQUIRE(ldr >= (long long)qk_heads * dk && ldk >= (long long)qk_heads * dk && ldv >= (long long)heads * dv, "matrix_state_scan: the rows are too short");
+    QI_REQUIRE(mode == 1 || (lw && w0 && ldw >= (long long)heads * dk), "matrix_state_scan: the decay's operands are missing");
+    QI_REQUIRE(mode != 0 || u, "matrix_state_scan: the bonus is missing");
+    QI_REQUIRE(mode != 2 || (bproj && ldb >= heads && unit_eps > 0.f && !decay_out), "matrix_state_scan: the delta rule needs beta's logits, a positive eps and runs entries in one piece");
     QI_REQUIRE(mode == 0 || lambda, "matrix_state_scan: the heads' decays are missing");
     QI_REQUIRE(state_stride >= (long long)heads * dk * dv, "matrix_state_scan: the slots of the state overlap");
     QI_REQUIRE(o || write_state, "matrix_state_scan: neither outputs nor the state are wanted");
@@ -496,7 +576,8 @@ extern "C" int qi_matrix_state_scan(int mode, const void* r, long long ldr, cons
     const dim3 grid(heads, n_entries, (dv + kColThreads - 1) / kColThreads), block(kColThreads);
 #define QI_MS(DKP, MODE)                                                                                                        \
     qi::launch(matrix_state_scan_kernel<T, DKP, MODE>, grid, block, 0, stream, (const T*)r, ldr, (const T*)k, ldk, (const T*)v, ldv, \
-               (const T*)lw, ldw, w0, u, lambda, state, state_stride, o, decay_out, write_state, q_start, start_pos, slot_ids, heads, dk, dv)
+               (const T*)lw, ldw, w0, u, lambda, state, state_stride, o, decay_out, write_state, q_start, start_pos, slot_ids, heads, dk, dv, \
+               (const T*)bproj, ldb, qk_heads, unit_eps, q_scale)
 #define QI_MS_DK(MODE)                              \
     if (dk <= 16) QI_MS(16, MODE);                  \
     else if (dk <= 32) QI_MS(32, MODE);             \
@@ -504,11 +585,21 @@ extern "C" int qi_matrix_state_scan(int mode, const void* r, long long ldr, cons
     else if (dk <= 128) QI_MS(128, MODE);           \
     else QI_MS(256, MODE)
     QI_DISPATCH_DTYPE(dtype, T, {
-        if (mode == 0) { QI_MS_DK(0); } else { QI_MS_DK(1); }
+        if (mode == 0) { QI_MS_DK(0); } else if (mode == 1) { QI_MS_DK(1); } else { QI_MS_DK(2); }
     });
 #undef QI_MS_DK
 #undef QI_MS
     return qi::check_launch("matrix_state_scan");
+}
+
+extern "C" int qi_matrix_state_scan(int mode, const void* r, long long ldr, const void* k, long long ldk, const void* v, long long ldv,
+                                    const void* lw, long long ldw, int dtype, const float* w0, const float* u, const float* lambda,
+                                    float* state, long long state_stride, float* o, float* decay_out, int write_state,
+                                    const int* q_start, const int* start_pos, const int* slot_ids, int n_entries, int heads,
+                                    int dk, int dv, cudaStream_t stream) {
+    QI_REQUIRE(mode == 0 || mode == 1, "matrix_state_scan: unknown mode %d", mode);
+    return qi_matrix_state_scan_ex(mode, r, ldr, k, ldk, v, ldv, lw, ldw, dtype, w0, u, lambda, state, state_stride, o, decay_out,
+                                   write_state, q_start, start_pos, slot_ids, n_entries, heads, dk, dv, nullptr, 0, heads, 1e-6f, 1.f, stream);
 }
 
 // seg_state float32 [segments, heads, dv, dk]; seg_decay float32 [segments, heads, dk]; state float32 [heads, dv, dk] a
@@ -516,7 +607,7 @@ extern "C" int qi_matrix_state_scan(int mode, const void* r, long long ldr, cons
 // Blocks of the scan kernel (mode, key size, operand type) that one SM holds at a time, or 0 when it cannot be told:
 // whoever cuts long entries into segments sizes them so that the launch fills whole waves.
 extern "C" int qi_matrix_state_scan_blocks_per_sm(int mode, int dk, int dtype) {
-    if ((mode != 0 && mode != 1) || !qi_matrix_state_scan_supported(dk) || (dtype != qi::kF32 && dtype != qi::kBF16)) return 0;
+    if (mode < 0 || mode > 2 || !qi_matrix_state_scan_supported(dk) || (dtype != qi::kF32 && dtype != qi::kBF16)) return 0;
     int blocks = 0;
 #define QI_MS_OCC(DKP, MODE) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, matrix_state_scan_kernel<T, DKP, MODE>, kColThreads, 0)
 #define QI_MS_OCC_DK(MODE)                          \
@@ -526,7 +617,7 @@ extern "C" int qi_matrix_state_scan_blocks_per_sm(int mode, int dk, int dtype) {
     else if (dk <= 128) QI_MS_OCC(128, MODE);       \
     else QI_MS_OCC(256, MODE)
     QI_DISPATCH_DTYPE(dtype, T, {
-        if (mode == 0) { QI_MS_OCC_DK(0); } else { QI_MS_OCC_DK(1); }
+        if (mode == 0) { QI_MS_OCC_DK(0); } else if (mode == 1) { QI_MS_OCC_DK(1); } else { QI_MS_OCC_DK(2); }
     });
 #undef QI_MS_OCC_DK
 #undef QI_MS_OCC

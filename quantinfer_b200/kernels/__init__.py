@@ -25,7 +25,7 @@ STATUS_NON_FINITE = 4
 STATUS_WAIT_TIMEOUT = 8
 STATUS_BAD_RANGE = 16
 
-ABI_VERSION = 12
+ABI_VERSION = 13
 
 
 def status_names(code: int) -> list:
@@ -232,6 +232,59 @@ def add_layernorm(resid: torch.Tensor, delta, gain: torch.Tensor, bias, eps: flo
           _ptr(bias), C.c_float(eps), _ptr(out), _code(out), _ptr(rows), n_out, h, int(bool(write_resid)), _stream())
 
 
+def scale_add_rmsnorm(resid: torch.Tensor, delta, alpha: float, gain: torch.Tensor, eps: float, copy=None) -> None:
+    """The norm that comes after the sum: resid = rmsnorm(alpha * resid + delta) * gain, in place and in 32-bit; `copy`
+    (or None) receives the new rows in its own type. resid float32 [n, h]; delta None, [n, h] or [splits, n, h] (partial
+    sums added in order); gain float32 [h]."""
+    _req(resid, "resid", torch.float32, 2)
+    _req(gain, "gain", torch.float32, 1)
+    n, h = resid.shape
+    splits, stride = 1, 0
+    if delta is not None:
+        _req(delta, "delta")
+        if delta.dim() == 3:
+            splits, stride = delta.shape[0], delta.shape[1] * delta.shape[2]
+        if tuple(delta.shape[-2:]) != (n, h) or delta.dim() not in (2, 3):
+            raise KernelError(f"scale_add_rmsnorm: delta {tuple(delta.shape)} does not match resid {tuple(resid.shape)}")
+    if gain.numel() != h:
+        raise KernelError(f"scale_add_rmsnorm: gain has {gain.numel()} elements, rows have {h}")
+    if copy is not None:
+        _req(copy, "copy", ndim=2)
+        if tuple(copy.shape) != (n, h):
+            raise KernelError(f"scale_add_rmsnorm: copy is {tuple(copy.shape)}, expected {(n, h)}")
+    _call("norm", "scale_add_rmsnorm", library().qi_scale_add_rmsnorm, _ptr(resid), _ptr(delta),
+          _code(delta) if delta is not None else F32, splits, C.c_longlong(stride), C.c_float(alpha), _ptr(gain), C.c_float(eps),
+          _ptr(copy), _code(copy) if copy is not None else F32, n, h, _stream())
+
+
+def normed_sum(a, b, gain_a, gain_b, eps: float, scale: float, out) -> None:
+    """out = scale * (rmsnorm(a) * gain_a + rmsnorm(b) * gain_b), each norm over a row, 32-bit; out float32 [n, h]. a and
+    b are [n, h] each, or [parts, n, h]: the partial sums of a split product, added here in order. Types may differ."""
+    _req(a, "a")
+    _req(b, "b")
+    _req(out, "out", torch.float32, 2)
+    _req(gain_a, "gain_a", torch.float32, 1)
+    _req(gain_b, "gain_b", torch.float32, 1)
+    n, h = out.shape
+    for t in (a, b):
+        if t.dim() not in (2, 3) or tuple(t.shape[-2:]) != (n, h) or not t.shape[0]:
+            raise KernelError("normed_sum: shapes differ")
+    if gain_a.numel() != h or gain_b.numel() != h:
+        raise KernelError("normed_sum: the gains do not fit the rows")
+    _call("norm", "normed_sum", library().qi_normed_sum, _ptr(a), a.shape[0] if a.dim() == 3 else 1, _code(a), _ptr(b),
+          b.shape[0] if b.dim() == 3 else 1, _code(b), _ptr(gain_a), _ptr(gain_b), C.c_float(eps), C.c_float(scale), _ptr(out), n, h,
+          _stream())
+
+
+def convert(x, out) -> None:
+    """out = x in out's type; x float32, same shape."""
+    _req(x, "x", torch.float32)
+    _req(out, "out")
+    if out.shape != x.shape:
+        raise KernelError("convert: shapes differ")
+    _call("other", "convert", library().qi_convert, _ptr(x), _ptr(out), _code(out), C.c_longlong(x.numel()), _stream())
+
+
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor) -> None:
     """out = rmsnorm(x) * gain over the last dimension; x and out of one type."""
     _req(x, "x")
@@ -336,8 +389,9 @@ def qk_norm_rope_kv(qkv, q_out, q_gain, k_gain, eps, cos, sin, rotary_dim, posit
 
 def attention_generic(q, out, k_pages, v_pages, block_table, positions, token_req, nq, nkv, d,
                       scale: float, window: int, status, chunk: int = 0, gate=None, softcap: float = 0.0,
-                      out_scale: float = 1.0) -> None:
-    """Causal paged GQA attention, 32-bit arithmetic, any span length and page size. Values may have another
+                      out_scale: float = 1.0, sink=None) -> None:
+    """Causal paged GQA attention, 32-bit arithmetic, any span length and page size. `sink` (float32 [nq] or None): the
+    softmax's denominator of head h holds exp(sink[h]) once more, with no key and no value. Values may have another
     size than keys (v_pages [pages, nkv, page_size, dv], out [n, nq dv]); `chunk` > 0: a query sees only the keys
     of its own chunk of that many positions (counted from the sequence's start); `gate` [n, >= nq dv] (a view whose
     rows may lie further apart): the result is multiplied by sigmoid(gate). `softcap` c > 0: a score s becomes
@@ -360,10 +414,14 @@ def attention_generic(q, out, k_pages, v_pages, block_table, positions, token_re
         if not gate.is_cuda or gate.dtype != q.dtype or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != out.shape:
             raise KernelError("attention: the gate must be [n, nq dv] in q's type with contiguous rows")
         ldg = gate.stride(0)
-    _call('attention', "attention_generic", library().qi_attention_generic_cap,
+    if sink is not None:
+        _req(sink, "sink", torch.float32, 1)
+        if sink.numel() != nq:
+            raise KernelError("attention: one sink a query head")
+    _call('attention', "attention_generic", library().qi_attention_generic_sink,
           _ptr(q), _ptr(out), _code(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
         block_table.shape[1], k_pages.shape[2], k_pages.shape[0], _ptr(positions), _ptr(token_req), n,
-        nq, nkv, d, dv, C.c_float(scale), C.c_float(softcap or 0.0), C.c_float(out_scale), int(window or 0), int(chunk or 0), _ptr(gate), C.c_longlong(ldg), _ptr(status), _stream())
+        nq, nkv, d, dv, C.c_float(scale), C.c_float(softcap or 0.0), C.c_float(out_scale), int(window or 0), int(chunk or 0), _ptr(gate), C.c_longlong(ldg), _ptr(sink), _ptr(status), _stream())
 
 
 def attention_mma_supported(nq: int, nkv: int, d: int) -> bool:
@@ -411,7 +469,7 @@ def attention_prefill_ranges(n_ctas: int, max_kv_len: int) -> int:
 def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos, tile_req, tile_q0,
                       nq, nkv, d, scale: float, window: int, status, use_tma: bool | None = None,
                       impl: str | None = None, max_kv_len: int = 0, key_ranges: int | None = None, chunk: int = 0,
-                      gate=None, softcap: float = 0.0, out_scale: float = 1.0) -> None:
+                      gate=None, softcap: float = 0.0, out_scale: float = 1.0, sink=None) -> None:
     """Causal paged GQA flash attention (bfloat16, head size 64 or 128) for spans of any
     length. `tile_req[i]`, `tile_q0[i]`: request index and first flat token of the i-th
     block of up to QUERY_TILE query rows.
@@ -424,8 +482,8 @@ def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos,
     contexts into key ranges over more CTAs (`key_ranges` forces a number). The tcgen05 kernel alone takes
     `chunk` (a query sees only the keys of its own chunk of that many positions, counted from the sequence's
     start), `gate` (bfloat16 [n, nq d], rows a multiple of 8 elements apart and 16-byte aligned: the output is
-    multiplied with its sigmoid), `softcap` c > 0 (a score s becomes c tanh(s / c)) and `out_scale` (a factor on the
-    result)."""
+    multiplied with its sigmoid), `softcap` c > 0 (a score s becomes c tanh(s / c)), `out_scale` (a factor on the
+    result) and `sink` (float32 [nq]: exp(sink[h]) once more in the softmax's denominator of head h)."""
     if impl is None and use_tma is not None:
         impl = "tma" if use_tma else "cpasync"
     _req(q, "q", torch.bfloat16, 2)
@@ -458,14 +516,16 @@ def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos,
             if not gate.is_cuda or gate.dtype != torch.bfloat16 or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != out.shape:
                 raise KernelError("attention_prefill: the gate must be bfloat16 [n, nq d] with contiguous rows")
             ldg = gate.stride(0)
-        _call('attention', "attention_prefill_tcgen05", library().qi_attention_prefill_tcgen05_ex,
+        if sink is not None:
+            _req(sink, "sink", torch.float32, 1)
+        _call('attention', "attention_prefill_tcgen05", library().qi_attention_prefill_tcgen05_sink,
               _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
             k_pages.shape[2], k_pages.shape[0], _ptr(q_start), _ptr(start_pos), _ptr(tile_req), _ptr(tile_q0),
             tile_req.numel(), q.shape[0], nq, nkv, d, C.c_float(scale), int(window or 0), int(chunk or 0), _ptr(gate),
-            C.c_longlong(ldg), ranges, _ptr(ws), _ptr(status), C.c_float(softcap or 0.0), C.c_float(out_scale), _stream())
+            C.c_longlong(ldg), ranges, _ptr(ws), _ptr(status), C.c_float(softcap or 0.0), C.c_float(out_scale), _ptr(sink), _stream())
         return
-    if chunk or gate is not None or softcap or out_scale != 1.0:
-        raise KernelError(f"attention_prefill: the {impl!r} kernel takes neither a chunk bound, a gate, a soft cap nor an output factor")
+    if chunk or gate is not None or softcap or out_scale != 1.0 or sink is not None:
+        raise KernelError(f"attention_prefill: the {impl!r} kernel takes neither a chunk bound, a gate, a soft cap, an output factor nor a sink")
     if impl not in ("tma", "cpasync"):
         raise KernelError(f"attention_prefill: unknown kernel {impl!r}")
     if impl == "tma":
@@ -927,6 +987,15 @@ def gated_sum(gates, b0, b1, y0, y1, out) -> None:
           _ptr(y0), _ptr(y1), _code(y0), _ptr(out), n, ch, _stream())
 
 
+def sigmoid_gate(x, gate) -> None:
+    """x *= sigmoid(gate) in place; x [n, c] contiguous; gate [n, c], possibly a block of columns of wider rows."""
+    _req(x, "x", ndim=2)
+    if not gate.is_cuda or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != x.shape:
+        raise KernelError("sigmoid_gate: the gate must match x, with contiguous rows")
+    _call("other", "sigmoid_gate", library().qi_sigmoid_gate, _ptr(x), _code(x), _ptr(gate), _code(gate), C.c_longlong(gate.stride(0)),
+          x.shape[0], x.shape[1], _stream())
+
+
 def softcap(x, cap: float) -> None:
     """x = cap * tanh(x / cap) in place; x float32."""
     _req(x, "x", torch.float32)
@@ -938,11 +1007,14 @@ def softcap(x, cap: float) -> None:
 
 
 def latent_prepare(proj, kv_offset, q_out, gain, eps: float, inv_freq, rot_dims: int, positions, token_req,
-                   block_table, cache, heads: int, d: int, r: int, rank: int, status) -> None:
+                   block_table, cache, heads: int, d: int, r: int, rank: int, status, half_split: bool = False,
+                   magnitude: float = 1.0) -> None:
     """From the fused projection's rows [heads x (d + r) | latent projection (rank + r) at column kv_offset]: rotates
     every head's r-part into q_out[:, h, rank:], and, unless kv_offset is None, normalises the latent (gain float32
     [rank]), rotates the shared key part and writes [latent | key part] into `cache` [pages, page_size, rank + r] at
-    each token's position. Pairs (2i, 2i + 1) of the part's first rot_dims coordinates turn by position * inv_freq[i]."""
+    each token's position. Pairs (2i, 2i + 1) of the part's first rot_dims coordinates, or (i, i + rot_dims / 2) when
+    `half_split`, turn by position * inv_freq[i]; cos and sin are multiplied by `magnitude`. The rows of `proj` may be
+    wider than what is read here."""
     _req(proj, "proj", ndim=2)
     _req(q_out, "q_out", ndim=3)
     n = proj.shape[0]
@@ -966,7 +1038,8 @@ def latent_prepare(proj, kv_offset, q_out, gain, eps: float, inv_freq, rot_dims:
           _ptr(proj), _code(proj), C.c_longlong(proj.shape[1]), -1 if kv_offset is None else int(kv_offset), _ptr(q_out),
           _code(q_out), _ptr(gain if kv_offset is not None else None), C.c_float(eps), _ptr(inv_freq if rot_dims else None),
           rot_dims, _ptr(positions), _ptr(token_req), _ptr(block_table if kv_offset is not None else None), max_blocks,
-          page_size, num_pages, _ptr(cache if kv_offset is not None else None), n, heads, d, r, rank, _ptr(status), _stream())
+          page_size, num_pages, _ptr(cache if kv_offset is not None else None), n, heads, d, r, rank, int(bool(half_split)),
+          C.c_float(magnitude), _ptr(status), _stream())
 
 
 def latent_attention_generic(q, out, cache, sink, block_table, positions, token_req, scale: float, window: int, status) -> None:
@@ -1100,15 +1173,26 @@ def concat_cast(a, b, out) -> None:
 
 
 def bias_rope_kv(proj, bias, q_out, inv_freq, rot: int, interleaved: bool, positions, token_req, block_table, page_size: int,
-                 k_pages, v_pages, nq: int, nkv: int, d: int, dv: int, status) -> None:
+                 k_pages, v_pages, nq: int, nkv: int, d: int, dv: int, status, q_gain=None, k_gain=None, norm_eps: float = 0.0,
+                 values_from_keys: bool = False) -> None:
     """proj [n, >= (nq + nkv) d + nkv dv] holds q | k | v (more columns may follow); bias float32 over those columns or
     None; the first `rot` coordinates of each q and k head turn by position * inv_freq[pair] (computed here in 32-bit:
-    no table, no limit on positions); q goes to q_out [n, nq d], k and v into the pages (None: nothing is written)."""
+    no table, no limit on positions); q goes to q_out [n, nq d], k and v into the pages (None: nothing is written).
+    q_gain, k_gain (float32 [nq d], [nkv d]; both or neither): all of q and all of k each pass one RMS norm with that gain
+    and `norm_eps` before the rotation. values_from_keys: the rows hold no v; a position's value is its key as
+    projected, before norm and rotation (dv = d)."""
     if not proj.is_cuda or proj.dim() != 2 or proj.stride(1) != 1:
         raise KernelError("bias_rope_kv: proj must be a CUDA tensor with contiguous rows")
     _req(q_out, "q_out", proj.dtype, 2)
     n = proj.shape[0]
-    cols = (nq + nkv) * d + nkv * dv
+    cols = (nq + nkv) * d + (0 if values_from_keys else nkv * dv)
+    if (q_gain is None) != (k_gain is None) or (values_from_keys and dv != d):
+        raise KernelError("bias_rope_kv: the norms of q and k come together; values that are keys have the keys' size")
+    if q_gain is not None:
+        _req(q_gain, "q_gain", torch.float32, 1)
+        _req(k_gain, "k_gain", torch.float32, 1)
+        if q_gain.numel() != nq * d or k_gain.numel() != nkv * d:
+            raise KernelError("bias_rope_kv: the gains do not fit q and k")
     if proj.shape[1] < cols or tuple(q_out.shape) != (n, nq * d):
         raise KernelError(f"bias_rope_kv: proj {tuple(proj.shape)} / q_out {tuple(q_out.shape)} do not match the heads")
     if bias is not None:
@@ -1129,10 +1213,10 @@ def bias_rope_kv(proj, bias, q_out, inv_freq, rot: int, interleaved: bool, posit
         if tuple(k_pages.shape[1:]) != (nkv, page_size, d) or tuple(v_pages.shape) != (k_pages.shape[0], nkv, page_size, dv):
             raise KernelError(f"bias_rope_kv: pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)} do not fit")
         num_pages, max_blocks = k_pages.shape[0], block_table.shape[1]
-    _call("rope", "bias_rope_kv", library().qi_bias_rope_kv, _ptr(proj), C.c_longlong(proj.stride(0)), _ptr(bias), _ptr(q_out),
+    _call("rope", "bias_rope_kv", library().qi_norm_rope_kv, _ptr(proj), C.c_longlong(proj.stride(0)), _ptr(bias), _ptr(q_out),
           _code(proj), _ptr(inv_freq if rot else None), rot, int(bool(interleaved)), _ptr(positions), _ptr(token_req),
-          _ptr(block_table), max_blocks, page_size, num_pages, _ptr(k_pages), _ptr(v_pages), n, nq, nkv, d, dv, _ptr(status),
-          _stream())
+          _ptr(block_table), max_blocks, page_size, num_pages, _ptr(k_pages), _ptr(v_pages), n, nq, nkv, d, dv, _ptr(q_gain),
+          _ptr(k_gain), C.c_float(norm_eps), int(bool(values_from_keys)), _ptr(status), _stream())
 
 
 def ssm_scan(xbc, raw_dt, dt_bias, a_log, d_skip, state, y, q_start, start_pos, slot_ids, heads: int, groups: int, P: int, N: int,
@@ -1259,7 +1343,8 @@ def token_shift(h, mu, state, out, token_req, q_start, start_pos, slot_ids) -> N
 
 
 def matrix_state_scan(mode: str, r, k, v, state, o, q_start, start_pos, slot_ids, heads: int, dk: int, dv: int, *, log_decay=None,
-                      decay_bias=None, bonus=None, head_decay=None, decay_out=None, write_state: bool = True) -> None:
+                      decay_bias=None, bonus=None, head_decay=None, decay_out=None, write_state: bool = True, beta=None,
+                      qk_heads: int | None = None, unit_eps: float = 1e-6, q_scale: float = 1.0) -> None:
     """A recurrence over a matrix state S [dk, dv] a head that decays and receives k_t v_t^T with every token.
     mode "channel_decay": o_t = S_(t-1)^T r_t + (sum_i r_i bonus_i k_i) v_t, then S_t = diag(w_t) S_(t-1) + k_t v_t^T with
     w_t = exp(-exp(log_decay_t + decay_bias)) per head and key channel. mode "head_decay": r, k, v pass silu first,
@@ -1267,16 +1352,31 @@ def matrix_state_scan(mode: str, r, k, v, state, o, q_start, start_pos, slot_ids
     columns of wider rows are fine); decay_bias, bonus float32 [heads dk]; head_decay float32 [heads]; state float32
     [slots, heads, dv, dk]; o float32 [n, heads dv], or None: the state moves on and nothing else is written. decay_out
     (or None): float32 [entries, heads, dk], receives the product of each entry's decays per key channel. write_state
-    False: the state is only read. The last three serve long entries cut into segments (`matrix_state_chain`)."""
-    if mode not in ("channel_decay", "head_decay"):
+    False: the state is only read. The last three serve long entries cut into segments (`matrix_state_chain`).
+    mode "delta": the gated delta rule. S' = diag(w_t) S_(t-1), u_t = beta_t (v_t - S'^T k_t), S_t = S' + k_t u_t^T,
+    o_t = S_t^T r_t, with r and k [n, qk_heads dk] made unit vectors per head (x / sqrt(sum x^2 + unit_eps)), r times
+    q_scale; heads / qk_heads heads share one head of r and k; beta = sigmoid of `beta` [n, heads]; w_t =
+    exp(-exp(head_decay_h) softplus(log_decay_t + decay_bias)) with head_decay the logarithm of each head's rate. Entries
+    run in one piece (the recurrence's factor is not diagonal), so `decay_out` is not offered."""
+    if mode not in ("channel_decay", "head_decay", "delta"):
         raise KernelError(f"matrix_state_scan: unknown mode {mode!r}")
     for t, name in ((r, "r"), (k, "k"), (v, "v")):
         _cols(t, name, r.dtype)
     n = r.shape[0]
-    if r.shape[1] != heads * dk or k.shape != r.shape or tuple(v.shape) != (n, heads * dv):
+    delta = mode == "delta"
+    qk_heads = (qk_heads or heads) if delta else heads
+    if qk_heads <= 0 or heads % qk_heads or r.shape[1] != qk_heads * dk or k.shape != r.shape or tuple(v.shape) != (n, heads * dv):
         raise KernelError("matrix_state_scan: r, k, v do not fit the heads")
     channel = mode == "channel_decay"
-    if channel:
+    if delta:
+        _cols(log_decay, "log_decay", r.dtype)
+        _cols(beta, "beta", r.dtype)
+        _req(decay_bias, "decay_bias", torch.float32)
+        _req(head_decay, "head_decay", torch.float32, 1)
+        if tuple(log_decay.shape) != (n, heads * dk) or tuple(beta.shape) != (n, heads) or decay_bias.numel() != heads * dk or (
+                head_decay.numel() != heads) or decay_out is not None:
+            raise KernelError("matrix_state_scan: the delta rule's operands do not fit the heads")
+    elif channel:
         _cols(log_decay, "log_decay", r.dtype)
         _req(decay_bias, "decay_bias", torch.float32)
         _req(bonus, "bonus", torch.float32)
@@ -1299,11 +1399,12 @@ def matrix_state_scan(mode: str, r, k, v, state, o, q_start, start_pos, slot_ids
         _req(decay_out, "decay_out", torch.float32, 3)
         if tuple(decay_out.shape) != (start_pos.numel(), heads, dk):
             raise KernelError("matrix_state_scan: decay_out must be [entries, heads, dk]")
-    _call("scan", "matrix_state_scan", library().qi_matrix_state_scan, 0 if channel else 1, _ptr(r), C.c_longlong(r.stride(0)), _ptr(k),
-          C.c_longlong(k.stride(0)), _ptr(v), C.c_longlong(v.stride(0)), _ptr(log_decay), C.c_longlong(log_decay.stride(0) if channel else 0),
+    _call("scan", "matrix_state_scan", library().qi_matrix_state_scan_ex, 2 if delta else 0 if channel else 1, _ptr(r),
+          C.c_longlong(r.stride(0)), _ptr(k), C.c_longlong(k.stride(0)), _ptr(v), C.c_longlong(v.stride(0)), _ptr(log_decay),
+          C.c_longlong(log_decay.stride(0) if (channel or delta) else 0),
           _code(r), _ptr(decay_bias), _ptr(bonus), _ptr(head_decay), _ptr(state), C.c_longlong(state.stride(0)), _ptr(o),
           _ptr(decay_out), int(bool(write_state)), _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), start_pos.numel(), heads, dk, dv,
-          _stream())
+          _ptr(beta), C.c_longlong(beta.stride(0) if delta else 0), qk_heads, C.c_float(unit_eps), C.c_float(q_scale), _stream())
 
 
 def matrix_state_chain(seg_state, seg_decay, state, entry_seg, start_pos, slot_ids) -> None:
@@ -1470,13 +1571,14 @@ def gated_attention_mma_supported(nq: int, nkv: int, d: int, dv: int) -> bool:
 
 
 def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv, scale: float, window: int, chunk: int, gate,
-                    status, impl: str | None = None, softcap: float = 0.0, out_scale: float = 1.0) -> None:
+                    status, impl: str | None = None, softcap: float = 0.0, out_scale: float = 1.0, sink=None) -> None:
     """Attention with separate key and value sizes, an optional chunk bound and an optional output gate, by the
     kernel that fits: "mma" (bfloat16, head sizes that are multiples of 8 up to 128: flash form on the tensor
     cores, tiles found on the device from the step's arrays) or "generic" (32-bit arithmetic, any sizes). A step
     with prompt portions whose keys and values are both of size 128 goes to "tcgen05": the portions' query tiles
     to the tcgen05 flash kernel (chunk bound and gate included), the single tokens in front of them to "mma".
-    `softcap` c > 0 (a score s becomes c tanh(s / c)) and `out_scale` (a factor on the result) are known to all three."""
+    `softcap` c > 0 (a score s becomes c tanh(s / c)), `out_scale` (a factor on the result) and `sink` (float32 [nq]:
+    exp(sink[h]) once more in the softmax's denominator of head h) are known to all three."""
     if impl is None and q.dtype == torch.bfloat16 and d == dv and not batch.all_decode and batch.tile_req.numel() and (
             gate is None or (gate.stride(0) % 8 == 0 and gate.data_ptr() % 16 == 0)) and attention_prefill_tcgen05_supported(
             nq, nkv, d, k_pages.shape[2], block_table.shape[1]):
@@ -1486,16 +1588,21 @@ def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv
         if lead:
             gated_attention(q[:lead], out[:lead], k_pages, v_pages, block_table[:lead], _LeadRows(batch, lead), nq, nkv, d, dv,
                             scale, window, chunk, gate[:lead] if gate is not None else None, status, impl="mma", softcap=softcap,
-                            out_scale=out_scale)
+                            out_scale=out_scale, sink=sink)
         return attention_prefill(q, out, k_pages, v_pages, block_table, batch.q_start, batch.start_pos, batch.tile_req,
                                  batch.tile_q0, nq, nkv, d, scale, window, status, impl="tcgen05", max_kv_len=batch.max_kv_len,
-                                 key_ranges=1 if chunk else None, chunk=chunk, gate=gate, softcap=softcap, out_scale=out_scale)
+                                 key_ranges=1 if chunk else None, chunk=chunk, gate=gate, softcap=softcap, out_scale=out_scale,
+                                 sink=sink)
     if impl is None:
         impl = "mma" if q.dtype == torch.bfloat16 and gated_attention_mma_supported(nq, nkv, d, dv) and (
             gate is None or gate.stride(0) % 2 == 0) else "generic"
     if impl == "generic":
         return attention_generic(q, out, k_pages, v_pages, block_table, batch.positions, batch.token_req, nq, nkv, d, scale,
-                                 window, status, chunk=chunk, gate=gate, softcap=softcap, out_scale=out_scale)
+                                 window, status, chunk=chunk, gate=gate, softcap=softcap, out_scale=out_scale, sink=sink)
+    if sink is not None:
+        _req(sink, "sink", torch.float32, 1)
+        if sink.numel() != nq:
+            raise KernelError("gated_attention: one sink a query head")
     _req(q, "q", torch.bfloat16, 2)
     _req(out, "out", torch.bfloat16, 2)
     _req(k_pages, "k_pages", torch.bfloat16, 4)
@@ -1511,8 +1618,8 @@ def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv
         if not gate.is_cuda or gate.dtype != q.dtype or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != out.shape:
             raise KernelError("gated_attention: the gate must be [n, nq dv] in q's type with contiguous rows")
         ldg = gate.stride(0)
-    _call("attention", "gated_attention_mma", library().qi_gated_attention_mma, _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages),
+    _call("attention", "gated_attention_mma", library().qi_gated_attention_mma_sink, _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages),
           _ptr(block_table), block_table.shape[1], k_pages.shape[2], k_pages.shape[0], _ptr(batch.q_start), _ptr(batch.start_pos),
           batch.n_requests, n, nq, nkv, d, dv, C.c_float(scale), C.c_float(softcap or 0.0), C.c_float(out_scale), int(window or 0),
-          int(chunk or 0), _ptr(gate), C.c_longlong(ldg),
+          int(chunk or 0), _ptr(gate), C.c_longlong(ldg), _ptr(sink),
           _ptr(status), _stream())

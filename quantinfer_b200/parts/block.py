@@ -247,6 +247,69 @@ class SandwichBlock(Part):
         return resid, PostNormed(self.ffn.forward(h), self.norm2b, m)
 
 
+class PostNormBlock(Part):
+    """The block whose norms come after the sums and replace the stream:
+
+        x = norm1(alpha * x + mixer(x)) ;  x = norm2(alpha * x + ffn(x))
+
+    The sublayers read the stream itself. Sum, norm and the stream's copy in the activation type (what the next sublayer's
+    projections read) are one kernel; the block hands that copy on to the next block as a :class:`StreamCopy`. The
+    feed-forward, with its norm, may be absent. The norms must offer `renorm` (the form that replaces the stream)."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.mixer_norm = build_part("norm", spec.mixer_norm, runtime)
+        self.mixer = build_part("mixer", spec.mixer, runtime)
+        self.ffn = build_part("ffn", spec.ffn, runtime) if spec.ffn is not None else None
+        self.ffn_norm = build_part("norm", spec.ffn_norm, runtime) if spec.ffn is not None else None
+        for n in (self.mixer_norm, self.ffn_norm):
+            if n is not None and not hasattr(n, "renorm"):
+                raise ConfigError("postnorm: a norm after the sum must be able to replace the stream (renorm)")
+        if hasattr(self.mixer, "keep_partials"):
+            self.mixer.keep_partials = True       # the norm's kernel adds a split product's partial sums itself
+        self._parts = tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None)
+
+    @classmethod
+    def needs_of_spec(cls, spec):
+        needs = {}
+        subs = [("norm", spec.mixer_norm), ("mixer", spec.mixer)]
+        if spec.ffn is not None:
+            subs += [("norm", spec.ffn_norm), ("ffn", spec.ffn)]
+        for cat, sub in subs:
+            needs.update(part_class(cat, sub).needs_of_spec(sub))
+        return needs
+
+    def load(self, tensors):
+        for p in self._parts:
+            p.load(tensors)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def mixer_state_need(self):
+        return getattr(self.mixer, "state_need", lambda: None)()
+
+    def forward(self, resid, delta, batch, cache):
+        from .norm import StreamCopy, settle
+
+        if isinstance(delta, StreamCopy):
+            x = delta.x
+        else:
+            pending = settle(resid, delta)
+            if pending is not None:          # a block of another kind came before: its output joins the stream first
+                kernels.scaled_sum(resid, pending, 1.0, 1.0, resid)
+            if self.runtime.dtype == torch.float32:
+                x = resid
+            else:
+                x = torch.empty(resid.shape, dtype=self.runtime.dtype, device=resid.device)
+                kernels.convert(resid, x)
+        x = self.mixer_norm.renorm(resid, self.mixer.forward(x, batch, cache), self.spec.alpha)
+        if self.ffn is not None:
+            x = self.ffn_norm.renorm(resid, self.ffn.forward(x), self.spec.alpha)
+        return resid, StreamCopy(x)
+
+
+register_part("block", "postnorm", PostNormBlock)
 register_part("block", "prenorm", PreNormBlock)
 register_part("block", "sandwich", SandwichBlock)
 register_part("block", "prenorm_conv", ConvPreNormBlock)

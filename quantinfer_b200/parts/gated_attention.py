@@ -7,7 +7,10 @@
     a               = softmax(cap(q k^T * scale) over the visible keys) v          cap(s) = c tanh(s / c), optional
     y               = (a * sigmoid(g) * out_scale) . Wo^T (+ b_o)
 
-Biases, the gate, the convolution, the cap and the factor are each optional (fields of the spec). The convolution's
+Biases, the gate, the convolution, the cap and the factor are each optional (fields of the spec). So are: a sink (the
+softmax's denominator holds exp(b_h) once more, b zero or the learned tensor `sink`); one RMS norm over the whole of q
+and one over the whole of k before the rotation (`q.norm`, `k.norm`); values that are the keys as projected, before
+norm and rotation (no `v` then). The convolution's
 last taps - 1 projected rows are the mixer's state of fixed size BESIDE its pages (`state_need`, handed back as
 `cache.mixer_state`).
 
@@ -44,8 +47,17 @@ class GatedAttention(Part):
             if v is not None and v <= 0:
                 raise ConfigError(f"gated_attention: {name} must be positive or None")
         self.H, self.G, self.d, self.dv = s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim
-        self.qkv_cols = (self.H + self.G) * self.d + self.G * self.dv
+        self.v_from_k = bool(getattr(s, "values_from_keys", False))
+        self.sink_kind, self.qk_norm = getattr(s, "sink", None), getattr(s, "qk_norm", None)
+        if self.v_from_k and (self.dv != self.d or getattr(s, "conv_taps", None) is not None or s.bias):
+            raise ConfigError("gated_attention: values that are the keys have the keys' size, no bias and no convolution")
+        if self.sink_kind not in (None, "zero", "learned") or self.qk_norm not in (None, "whole"):
+            raise ConfigError(f"gated_attention: sink {self.sink_kind!r} / qk_norm {self.qk_norm!r} are not known")
+        self.sink = self.q_gain = self.k_gain = None
+        self.qkv_cols = (self.H + self.G) * self.d + (0 if self.v_from_k else self.G * self.dv)
         self.proj = Linear(runtime, self.qkv_cols + (self.H * self.dv if s.out_gate else 0), s.hidden_size, s.prefix + "q+k+v+g")
+        if self.sink_kind == "zero":
+            self.sink = torch.zeros(self.H, dtype=torch.float32, device=runtime.device)
         self.o = Linear(runtime, s.hidden_size, self.H * self.dv, s.prefix + "o")
         self.bias = self.out_bias = self.inv_freq = self.conv_w = None
         self.taps = getattr(s, "conv_taps", None)
@@ -63,7 +75,13 @@ class GatedAttention(Part):
     @classmethod
     def needs_of_spec(cls, s):
         p, H, G, d, dv, w = s.prefix, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, s.hidden_size
-        needs = {p + "q": TensorNeed((H * d, w)), p + "k": TensorNeed((G * d, w)), p + "v": TensorNeed((G * dv, w))}
+        needs = {p + "q": TensorNeed((H * d, w)), p + "k": TensorNeed((G * d, w))}
+        if not getattr(s, "values_from_keys", False):
+            needs[p + "v"] = TensorNeed((G * dv, w))
+        if getattr(s, "qk_norm", None) == "whole":
+            needs.update({p + "q.norm": TensorNeed((H * d,), "gain", "gain"), p + "k.norm": TensorNeed((G * d,), "gain", "gain")})
+        if getattr(s, "sink", None) == "learned":
+            needs[p + "sink"] = TensorNeed((H,), "gain", "normal")
         if s.out_gate:
             needs[p + "g"] = TensorNeed((H * dv, w))
         needs[p + "o"] = TensorNeed((w, H * dv))
@@ -77,7 +95,11 @@ class GatedAttention(Part):
 
     def load(self, tensors):
         p, s = self.spec.prefix, self.spec
-        ws = [tensors[p + n] for n in ("q", "k", "v") + (("g",) if s.out_gate else ())]
+        ws = [tensors[p + n] for n in ("q", "k") + (() if self.v_from_k else ("v",)) + (("g",) if s.out_gate else ())]
+        if self.qk_norm == "whole":
+            self.q_gain, self.k_gain = self._gain(tensors[p + "q.norm"]), self._gain(tensors[p + "k.norm"])
+        if self.sink_kind == "learned":
+            self.sink = self._gain(tensors[p + "sink"])
         if len({t.dtype for t in ws}) > 1:
             ws = [t.to(torch.float32) for t in ws]
         self.proj.load(torch.cat(ws, dim=0))
@@ -113,12 +135,14 @@ class GatedAttention(Part):
         q = torch.empty((n, self.H * self.d), dtype=x.dtype, device=x.device)
         kernels.bias_rope_kv(proj, self.bias, q, self.inv_freq, self.rot, self.interleaved, batch.positions, batch.token_req,
                              table, cache.page_size, cache.k_pages if cache.writes else None,
-                             cache.v_pages if cache.writes else None, self.H, self.G, self.d, self.dv, rt.status)
+                             cache.v_pages if cache.writes else None, self.H, self.G, self.d, self.dv, rt.status,
+                             q_gain=self.q_gain, k_gain=self.k_gain, norm_eps=getattr(s, "qk_norm_eps", 0.0),
+                             values_from_keys=self.v_from_k)
         out = torch.empty((n, self.H * self.dv), dtype=x.dtype, device=x.device)
         gate = gate_src[:, self.qkv_cols:] if s.out_gate else None
         kernels.gated_attention(q, out, cache.k_pages, cache.v_pages, table, batch, self.H, self.G, self.d, self.dv, s.scale,
                                 s.window or 0, s.chunk or 0, gate, rt.status, softcap=getattr(s, "softcap", None) or 0.0,
-                                out_scale=getattr(s, "out_scale", 1.0))
+                                out_scale=getattr(s, "out_scale", 1.0), sink=self.sink)
         return self.o(out, keep_partials=True)
 
 

@@ -46,9 +46,21 @@ class PostNormed:
         return None
 
 
+class StreamCopy:
+    """Nothing is pending: the stream is up to date, and `x` is the stream once more in the activation type, as the
+    norm that wrote the stream last left it beside it, for whoever reads the stream next."""
+
+    def __init__(self, x):
+        self.x = x
+
+    def apply(self, resid):
+        return None
+
+
 def settle(resid, delta):
-    """`delta` as something every norm takes: a pending :class:`PostNormed` is added to the stream now."""
-    return delta.apply(resid) if isinstance(delta, PostNormed) else delta
+    """`delta` as something every norm takes: a pending :class:`PostNormed` is added to the stream now; a
+    :class:`StreamCopy` has nothing to add."""
+    return delta.apply(resid) if isinstance(delta, (PostNormed, StreamCopy)) else delta
 
 
 class RMSNorm(Part):
@@ -71,6 +83,27 @@ class RMSNorm(Part):
         return out
 
     __call__ = forward
+
+
+class OnePlusRMSNorm(RMSNorm):
+    """RMS norm whose weight is stored around zero: out = x / sqrt(mean(x^2) + eps) * (1 + w), w the tensor named by the
+    spec's `prefix` itself. 1 + w is formed once, in 32-bit, at load. Besides the pre-norm form of every norm it offers
+    the form that comes AFTER a sum and replaces the stream (`renorm`)."""
+
+    @classmethod
+    def needs_of_spec(cls, spec):
+        return {spec.prefix: TensorNeed((spec.size,), "gain", "zeros")}
+
+    def load(self, tensors):
+        self.gain = self._gain(tensors[self.spec.prefix].to(torch.float32) + 1.0)
+
+    def renorm(self, resid, delta, alpha: float):
+        """resid <- norm(alpha * resid + delta), in place and in 32-bit; returns the new stream in the activation type
+        (the stream itself when that type is float32)."""
+        delta = settle(resid, delta)
+        copy = None if self.runtime.dtype == torch.float32 else torch.empty(resid.shape, dtype=self.runtime.dtype, device=resid.device)
+        kernels.scale_add_rmsnorm(resid, delta, alpha, self.gain, self.spec.eps, copy)
+        return resid if copy is None else copy
 
 
 class ScalarRMSNorm(RMSNorm):
@@ -170,3 +203,4 @@ register_part("norm", "rmsnorm", RMSNorm)
 register_part("norm", "layernorm", LayerNorm)
 register_part("norm", "dyt", DynamicTanh)
 register_part("norm", "rmsnorm_scalar", ScalarRMSNorm)
+register_part("norm", "rmsnorm_one_plus", OnePlusRMSNorm)

@@ -5,6 +5,10 @@ spec (applied by the branch before its output projection, so the sum needs no fa
 pages: its need is this mixer's `cache_need`. Everything else the branches keep is of fixed size: a branch's own
 entry (when its `cache_need` is a StateNeed) and what a branch keeps beside its pages (`state_need`) are laid side by
 side in ONE row of 32-bit numbers, this mixer's `state_need`, and each branch is handed its part of it.
+
+With `out_norm_names` in the spec each branch's output first passes an RMS norm over the model width (a gain per branch),
+and `sum_scale` multiplies the sum; norms, factor and sum are one kernel, which also adds the partial sums of the
+branches' output projections.
 """
 
 from __future__ import annotations
@@ -15,6 +19,7 @@ from .. import kernels
 from ..cache.manager import CacheView
 from ..cache.needs import StateNeed
 from ..errors import ConfigError
+from ..weights.loader import TensorNeed
 from .base import Part, build_part, part_class, register_part
 
 
@@ -46,17 +51,26 @@ class ParallelMixers(Part):
                     at += (_floats(need) + 3) // 4 * 4          # every part starts at a 16-byte boundary
             self._layout.append(spans)
         self._floats = at
+        self.out_gains = None
+        names = getattr(spec, "out_norm_names", None)
+        if names is not None and (len(names) != 2 or not getattr(spec, "hidden_size", None)):
+            raise ConfigError("parallel_mixers: norms on the branches' outputs need two gain names and the model width")
 
     @classmethod
     def needs_of_spec(cls, spec):
         needs = {}
         for sub in (spec.left, spec.right):
             needs.update(part_class("mixer", sub).needs_of_spec(sub))
+        for name in getattr(spec, "out_norm_names", None) or ():
+            needs[name] = TensorNeed((spec.hidden_size,), "gain", "gain")
         return needs
 
     def load(self, tensors):
         for b in self.branches:
             b.load(tensors)
+        names = getattr(self.spec, "out_norm_names", None)
+        if names is not None:
+            self.out_gains = tuple(self._gain(tensors[n]) for n in names)
 
     def cache_need(self):
         return self._paged[1] if self._paged is not None else None
@@ -83,7 +97,11 @@ class ParallelMixers(Part):
                 view = CacheView(cache.entry, state=self._part_of(row, own), writes=cache.writes, mixer_state=self._part_of(row, beside))
             outs.append(b.forward(x, batch, view))      # whole, or K-split partial sums [parts, n, h]: added in 32-bit below
         out = torch.empty(outs[0].shape[-2:], dtype=torch.float32, device=x.device)
-        kernels.scaled_sum(outs[0], outs[1], 1.0, 1.0, out)
+        scale = getattr(self.spec, "sum_scale", 1.0)
+        if self.out_gains is not None:
+            kernels.normed_sum(outs[0], outs[1], self.out_gains[0], self.out_gains[1], self.spec.out_norm_eps, scale, out)
+        else:
+            kernels.scaled_sum(outs[0], outs[1], scale, scale, out)
         return out
 
 

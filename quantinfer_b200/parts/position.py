@@ -16,11 +16,38 @@ between layers with the same angles.
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .. import kernels
 from ..errors import ConfigError
 from .base import Part, register_part
+
+
+def direct_frequencies(spec):
+    """(one frequency a pair as a float32 tensor on the CPU, factor on cos and sin) of a :class:`RotarySpec` whose angles
+    are computed where they are used. Plain: theta^(-2i / rotary_dim) and 1. With `stretch` = (factor, original, fast,
+    slow): with where(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta) the pair's number at which a pair turns t
+    times over `original` positions, lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), rotary_dim - 1) and
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns by f_i / factor * ramp_i + f_i (1 - ramp_i), and cos
+    and sin are multiplied by 0.1 ln(factor) + 1. Evaluated in 64-bit and rounded once."""
+    dims = spec.rotary_dim
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * i / float(dims))
+    stretch = getattr(spec, "stretch", None)
+    if stretch is None:
+        return f.to(torch.float32), 1.0
+    factor, original, fast, slow = (float(x) for x in stretch)
+    if factor <= 0.0 or original <= 0.0 or fast <= 0.0 or slow <= 0.0 or spec.theta <= 1.0:
+        raise ConfigError("a stretched rotation needs positive factor, original, fast and slow, and a base above one")
+
+    def where(turns):
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(spec.theta)))
+
+    lo, hi = max(math.floor(where(fast)), 0), min(math.ceil(where(slow)), dims - 1)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return (f / factor * ramp + f * (1.0 - ramp)).to(torch.float32), 0.1 * math.log(factor) + 1.0
 
 
 class RopeHalfSplit(Part):
