@@ -95,15 +95,22 @@ def softcap(s, cap):
     return cap * torch.tanh(s / cap) if cap else s
 
 
+def rotate_part(x, m):
+    """The rotated part of a latent-attention query or key: halves paired, frequencies stretched where the mixer says so."""
+    rot = m.get("rot")
+    if not rot or not rot["dims"]:
+        return x
+    freqs, mag = pair_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
+    return rotate(x, torch.arange(x.shape[0]), rot["dims"], freqs, mag, "half")
+
+
 def latent_rows(h, m, w, p, eps):
     """What a layer with a latent projection caches: the normed latent [T, kv_rank] and the rotated shared key part."""
     T = h.shape[0]
     R, r = m["kv_rank"], m["rot_dim"]
     z = h @ f64(w[p + "dkv"]).T
     c = norm_plain(z[:, :R], w[p + "dkv.norm"], eps)
-    freqs, mag = pair_frequencies(m["rot"]["dims"], m["rot"]["base"], m["rot"].get("scaling"))
-    kr = rotate(z[:, R:R + r], torch.arange(T), m["rot"]["dims"], freqs, mag, "half")
-    return c, kr
+    return c, rotate_part(z[:, R:R + r], m)
 
 
 def latent_attention(h, m, w, p, eps, latent):
@@ -112,8 +119,7 @@ def latent_attention(h, m, w, p, eps, latent):
     H, d, r, e, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     c, kr = latent
     q = (h @ f64(w[p + "q"]).T).view(T, H, d + r)
-    freqs, mag = pair_frequencies(m["rot"]["dims"], m["rot"]["base"], m["rot"].get("scaling"))
-    qr = rotate(q[..., d:], torch.arange(T), m["rot"]["dims"], freqs, mag, "half")
+    qr = rotate_part(q[..., d:], m)
     k = (c @ f64(w[p + "uk"]).T).view(T, H, d)
     v = (c @ f64(w[p + "uv"]).T).view(T, H, e)
     scores = (torch.einsum("ihd,jhd->hij", q[..., :d], k) + torch.einsum("ihd,jd->hij", qr, kr)) * m["scale"]

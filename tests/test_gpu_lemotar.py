@@ -1,0 +1,656 @@
+"""The Lemotar design on the GPU against the plain implementation (tests/plain/plain_lemotar.py): every mechanism
+alone, then whole models replayed whole, token by token, in portions down to two tokens and mixed with other
+requests on a pool so small that pages and slots are used again; generation through the scheduler.
+
+Where random weights would hide a fault the inputs are made so that it shows: one position whose value or key stands
+out for every query that sees it and for none beyond the window, sinks that take a good part of a row's weight,
+scores beyond the cap, a recurrent state carried over hundreds of steps, a slot whose earlier owner left its state."""
+
+import json
+import math
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import random_tokens
+from lemotar_tools import CONFIGS, PAGE_SIZES, clean, draw_weights, latent, left, make, model, parallel, plain_rows, right, write_folder
+from plain import plain_lemotar as plain
+from trace_tools import ROOT, collect, mixed_trace, portions_trace, round64, run_trace_engine, tail_trace, whole_trace
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+# |engine - plain float64| on logits of a few units. float32: the order of sums and the device's exp, tanh, sin, cos
+# (measured: median 2e-6 to 1.4e-5, worst 7.7e-5 where alpha is one; the bound is three times the worst). bfloat16: most rows within three
+# times the median, a few of a hundred beyond it, none beyond 1.5.
+TOL_F32 = 2.3e-4
+TOL_BF16 = {"P": 0.25, "Q": 0.5, "R": 0.25}       # Q: alpha one, so a sublayer's rounding weighs as much as the stream (median 0.16)
+BF16_ROWS_BEYOND, BF16_WORST = 0.04, 1.5
+LENGTHS = {"P": [70, 45, 100, 33, 2, 64, 17, 1], "Q": [130, 64, 97, 33, 200, 5], "R": [50, 33, 80, 17, 64, 9]}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("lemotar")
+    return {name: make(root / name, name) for name in CONFIGS}
+
+
+def _requests(name):
+    v = CONFIGS[name]["vocab"]
+    return {f"{name}{i}": random_tokens(n, v, seed=37 * i + n) for i, n in enumerate(LENGTHS[name])}
+
+
+_expected = {}
+
+
+def _expect(models, name):
+    if name not in _expected:
+        _, cfg, w = models[name]
+        _expected[name] = plain_rows(cfg, w, _requests(name))
+    return _expected[name]
+
+
+def _compare(got, expect, name, dtype, what=""):
+    assert set(got) == set(expect)
+    errs = {k: float(np.abs(got[k].astype(np.float64) - expect[k].astype(np.float64)).max()) for k in expect}
+    worst = max(errs, key=errs.get)
+    print(f"measured {name} {dtype} {what}: median {np.median(list(errs.values())):.3g}, worst {errs[worst]:.3g} at {worst}")
+    if dtype == "float32":
+        assert errs[worst] <= TOL_F32, f"worst difference {errs[worst]} at (request, position) {worst}"
+        return
+    beyond = sorted(k for k in errs if errs[k] > TOL_BF16[name])
+    assert len(beyond) <= max(1, BF16_ROWS_BEYOND * len(errs)) and errs[worst] <= BF16_WORST, (len(beyond), len(errs), errs[worst], worst)
+
+
+def _d(t):
+    return t.to(DEV)
+
+
+def _i(v):
+    return torch.tensor(v, dtype=torch.int32, device=DEV)
+
+
+def _entries(lens, starts):
+    """The step arrays of entries with these lengths and first positions, each in its own slot."""
+    q0 = [0] + np.cumsum(lens).tolist()
+    token_req = [e for e, n in enumerate(lens) for _ in range(n)]
+    return _i(q0), _i(starts), _i(list(range(len(lens)))), _i(token_req)
+
+
+# ---------------------------------------------------------------- small kernels against their formulas
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("h", [44, 64, 1000, 4104])
+@pytest.mark.parametrize("parts", [None, 1, 3])
+def test_the_norm_after_the_sum(dtype, h, parts):
+    """stream <- norm(alpha stream + delta) with the gain 1 + w, delta absent, whole or as partial sums; the stream in
+    32-bit and its copy in the activation type."""
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(h)
+    n, alpha, eps = 5, 1.7, 3e-6
+    resid = torch.randn(n, h) * 2.0
+    gain = 1.0 + 0.2 * torch.randn(h)
+    delta = None if parts is None else (torch.randn(n, h).to(dtype) if parts == 1 else torch.randn(parts, n, h))
+    x = alpha * resid.double() + (0 if delta is None else delta.double() if parts == 1 else delta.double().sum(0))
+    ref = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * gain.double()
+    r = _d(resid.clone())
+    copy = None if dtype == torch.float32 else torch.empty(n, h, dtype=dtype, device=DEV)
+    k.scale_add_rmsnorm(r, None if delta is None else _d(delta), alpha, _d(gain), eps, copy)
+    assert float((r.cpu().double() - ref).abs().max()) < 2e-5
+    if copy is not None:
+        assert torch.equal(copy.cpu(), r.cpu().to(dtype))
+
+
+@pytest.mark.parametrize("ka, kb", [(1, 1), (3, 1), (2, 4)])
+def test_the_sum_of_two_normed_branches(ka, kb):
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(ka * 7 + kb)
+    n, h, eps, s = 6, 44, 1e-5, 0.5
+    a = torch.randn(ka, n, h) if ka > 1 else torch.randn(n, h).to(torch.bfloat16)
+    b = torch.randn(kb, n, h) * 3.0 if kb > 1 else (torch.randn(n, h) * 3.0)
+    ga, gb = 1.0 + 0.3 * torch.randn(h), 1.0 + 0.3 * torch.randn(h)
+    out = torch.empty(n, h, dtype=torch.float32, device=DEV)
+    k.normed_sum(_d(a), _d(b), _d(ga), _d(gb), eps, s, out)
+    A, B = (a.double().sum(0) if ka > 1 else a.double()), (b.double().sum(0) if kb > 1 else b.double())
+    ref = s * (plain.norm_plain(A, ga, eps) + plain.norm_plain(B, gb, eps))
+    assert float((out.cpu().double() - ref).abs().max()) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_output_gate_and_the_conversion(dtype):
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(3)
+    x, wide = torch.randn(7, 21).to(dtype), torch.randn(7, 40).to(dtype)
+    xd = _d(x.clone())
+    k.sigmoid_gate(xd, _d(wide)[:, 11:32])
+    ref = x.double() * torch.sigmoid(wide[:, 11:32].double())
+    assert float((xd.cpu().double() - ref).abs().max()) < (1e-6 if dtype == torch.float32 else 0.02)
+    f = torch.randn(5, 33)
+    out = torch.empty(5, 33, dtype=dtype, device=DEV)
+    k.convert(_d(f), out)
+    assert torch.equal(out.cpu(), f.to(dtype))
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
+@pytest.mark.parametrize("H, G, d, rot", [(6, 3, 10, 4), (2, 1, 16, 16), (3, 3, 8, 0)])
+def test_whole_projection_norms_rotation_and_values_from_keys(interleaved, H, G, d, rot):
+    """q and k each normed as a whole before the rotation; the cached value is the key as projected; columns beyond q | k
+    are left alone; pages in shuffled order."""
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(H * d + rot)
+    page, lens, starts, eps = 8, [5, 1, 9], [0, 13, 6], 3e-6
+    n, B = sum(lens), len(lens)
+    proj = torch.randn(n, (H + G) * d + 5) * 1.5
+    qg, kg = 1.0 + 0.3 * torch.randn(H * d), 1.0 + 0.3 * torch.randn(G * d)
+    inv = 300.0 ** (-2.0 * torch.arange(rot // 2).double() / rot) if rot else None
+    blocks = 3
+    table = torch.randperm(B * blocks + 2)[:B * blocks].view(B, blocks).to(torch.int32)
+    kp = torch.zeros(B * blocks + 2, G, page, d, device=DEV)
+    vp = torch.zeros_like(kp)
+    q_out = torch.empty(n, H * d, device=DEV)
+    q0, sp, _, token_req = _entries(lens, starts)
+    positions = [s0 + i for s0, ln in zip(starts, lens) for i in range(ln)]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    k.bias_rope_kv(_d(proj), None, q_out, _d(inv.float()) if rot else None, rot, interleaved, _i(positions), token_req, _d(table), page, kp, vp,
+                   H, G, d, d, status, q_gain=_d(qg), k_gain=_d(kg), norm_eps=eps, values_from_keys=True)
+    assert int(status.item()) == 0
+    pos = torch.tensor(positions)
+    layout = "interleaved" if interleaved else "half"
+    qn = plain.norm_plain(proj[:, :H * d].double(), qg, eps).view(n, H, d)
+    kn = plain.norm_plain(proj[:, H * d:(H + G) * d].double(), kg, eps).view(n, G, d)
+    if rot:
+        qn, kn = plain.rotate(qn, pos, rot, inv, 1.0, layout), plain.rotate(kn, pos, rot, inv, 1.0, layout)
+    assert float((q_out.cpu().double().view(n, H, d) - qn).abs().max()) < 2e-5
+    for t in range(n):
+        e, p = int(token_req[t]), positions[t]
+        pg = int(table[e, p // page])
+        assert float((kp[pg, :, p % page].cpu().double() - kn[t]).abs().max()) < 2e-5
+        assert torch.equal(vp[pg, :, p % page].cpu(), proj[t, H * d:(H + G) * d].view(G, d))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads, qk_heads, dk, dv", [(4, 2, 6, 6), (2, 2, 32, 32), (2, 1, 40, 70), (2, 2, 100, 8), (1, 1, 130, 20), (4, 1, 16, 130)])
+def test_the_delta_rule_kernel(dtype, heads, qk_heads, dk, dv):
+    """Keys of 6 to 130 numbers (padded to the next size the kernel has), more value columns than a block takes, value
+    heads that share a head of q and k, entries of 1, 2, 19 and 45 tokens, slots with and without an earlier state."""
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(dk + dv)
+    lens, starts = [1, 19, 2, 45], [3, 0, 0, 11]
+    n = sum(lens)
+    q = (torch.randn(n, qk_heads * dk + 3) * 0.7).to(dtype)
+    kk = (torch.randn(n, qk_heads * dk) * 0.7).to(dtype)
+    v = (torch.randn(n, heads * dv + 1) * 0.7).to(dtype)
+    lw = (torch.randn(n, heads * dk) * 0.8).to(dtype)
+    bl = (torch.randn(n, heads + 2) * 1.5).to(dtype)
+    dt_bias, a_log = -3.0 + 3.0 * torch.rand(heads * dk), -1.0 + 2.0 * torch.rand(heads)
+    state = torch.randn(4, heads * dv * dk + 4) * 0.3
+    q0, sp, slots, _ = _entries(lens, starts)
+    o = torch.empty(n, heads * dv, dtype=torch.float32, device=DEV)
+    st = _d(state.clone())
+    S_dev = st[:, :heads * dv * dk].unflatten(1, (heads, dv, dk))
+    qs = 0.37
+    k.matrix_state_scan("delta", _d(q)[:, 3:], _d(kk), _d(v)[:, :heads * dv], S_dev, o, q0, sp, slots, heads, dk, dv, log_decay=_d(lw),
+                        decay_bias=_d(dt_bias), head_decay=_d(a_log), beta=_d(bl)[:, 1:1 + heads], qk_heads=qk_heads, unit_eps=1e-6, q_scale=qs)
+    a = 0
+    for e, ln in enumerate(lens):
+        group = torch.arange(heads) // (heads // qk_heads)
+        S0 = state[e, :heads * dv * dk].double().view(heads, dv, dk).transpose(1, 2) if starts[e] > 0 else torch.zeros(heads, dk, dv, dtype=torch.float64)
+        rows = slice(a, a + ln)
+        qq = plain.unit_vectors(q[rows, 3:].double().view(ln, qk_heads, dk))[:, group] * qs
+        kn = plain.unit_vectors(kk[rows].double().view(ln, qk_heads, dk))[:, group]
+        beta = torch.sigmoid(bl[rows, 1:1 + heads].double())
+        rate = torch.nn.functional.softplus(lw[rows].double() + dt_bias.double()).view(ln, heads, dk)
+        g = torch.exp(-torch.exp(a_log.double())[None, :, None] * rate)
+        S = S0.clone()
+        for t in range(ln):
+            S = S * g[t][:, :, None]
+            u = beta[t][:, None] * (v[a + t, :heads * dv].double().view(heads, dv) - torch.einsum("hkv,hk->hv", S, kn[t]))
+            S = S + kn[t][:, :, None] * u[:, None, :]
+            ref = torch.einsum("hkv,hk->hv", S, qq[t]).reshape(-1)
+            assert float((o[a + t].cpu().double() - ref).abs().max()) < 2e-4 * max(1.0, float(ref.abs().max())), (e, t)
+        got_S = st[e, :heads * dv * dk].cpu().double().view(heads, dv, dk).transpose(1, 2)
+        assert float((got_S - S).abs().max()) < 2e-4 * max(1.0, float(S.abs().max()))
+        assert torch.equal(st[e, heads * dv * dk:].cpu(), state[e, heads * dv * dk:])
+        a += ln
+
+
+def _attention_case(H, G, d, window, page, lens, starts, seed):
+    torch.manual_seed(seed)
+    B, n = len(lens), sum(lens)
+    ctx = [s + l for s, l in zip(starts, lens)]
+    blocks = max(-(-c // page) for c in ctx)
+    table = torch.randperm(B * blocks + 3)[:B * blocks].view(B, blocks).to(torch.int32)
+    kp = torch.zeros(B * blocks + 3, G, page, d)
+    vp = torch.zeros(B * blocks + 3, G, page, d)
+    keys = [(torch.randn(c, G, d) * 1.2).to(torch.bfloat16).float() for c in ctx]
+    vals = [torch.randn(c, G, d).to(torch.bfloat16).float() for c in ctx]
+    q = (torch.randn(n, H, d) * 1.2).to(torch.bfloat16).float()
+    sink = torch.randn(H) * 1.5 + 3.0
+    scale, cap = 0.8 / math.sqrt(d), 2.0
+    ref = torch.zeros(n, H, d, dtype=torch.float64)
+    a, sink_share = 0, []
+    for e in range(B):
+        for j in range(ctx[e]):
+            kp[table[e, j // page], :, j % page] = keys[e][j]
+            vp[table[e, j // page], :, j % page] = vals[e][j]
+        for t in range(lens[e]):
+            pos = starts[e] + t
+            lo = max(0, pos - window + 1) if window else 0
+            for hq in range(H):
+                g = hq // (H // G)
+                s = cap * torch.tanh((keys[e][lo:pos + 1, g].double() @ q[a + t, hq].double()) * scale / cap)
+                m = max(float(s.max()), float(sink[hq]))
+                w = torch.exp(s - m)
+                den = w.sum() + math.exp(float(sink[hq]) - m)
+                sink_share.append(math.exp(float(sink[hq]) - m) / float(den))
+                ref[a + t, hq] = (w / den) @ vals[e][lo:pos + 1, g].double()
+        if window:                               # pages wholly before every row's window may hold anything
+            for b in range(max(0, starts[e] - window + 1) // page):
+                kp[table[e, b]] = vp[table[e, b]] = float("nan")
+        a += lens[e]
+    assert np.median(sink_share) > 0.02         # the premise: leaving the sink out changes every row
+    return q, kp, vp, table, sink, scale, cap, ref, ctx
+
+
+@pytest.mark.parametrize("impl, dtype", [("generic", torch.float32), ("generic", torch.bfloat16), ("mma", torch.bfloat16)])
+@pytest.mark.parametrize("H, G, d, window", [(4, 2, 16, 24), (2, 1, 64, 0), (3, 3, 40, 9), (2, 2, 8, 17)])
+def test_a_sink_and_a_window_in_both_attention_kernels(impl, dtype, H, G, d, window):
+    """One more term in the denominator, a sliding window whose edge lies inside a page, capped scores, pages in
+    shuffled order, a decode token in front of two portions, NaN in the pages no row may look at."""
+    from types import SimpleNamespace
+    from quantinfer_b200 import kernels as k
+
+    page, lens, starts = 8, [1, 37, 20], [50, 0, 19]
+    q, kp, vp, table, sink, scale, cap, ref, ctx = _attention_case(H, G, d, window, page, lens, starts, H * d + window)
+    n, B = sum(lens), len(lens)
+    q0, sp, _, token_req = _entries(lens, starts)
+    batch = SimpleNamespace(q_start=q0, start_pos=sp, n_requests=B, token_req=token_req, all_decode=False, n_lead_decode=1,
+                            positions=_i([s0 + i for s0, ln in zip(starts, lens) for i in range(ln)]), max_kv_len=max(ctx),
+                            tile_req=_i([]), tile_q0=_i([]))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((n, H * d), float("nan"), dtype=dtype, device=DEV)
+    k.gated_attention(_d(q.view(n, H * d).to(dtype)), out, _d(kp.to(dtype)), _d(vp.to(dtype)), _d(table), batch, H, G, d, d, scale, window, 0,
+                      None, status, impl=impl, softcap=cap, sink=_d(sink))
+    assert int(status.item()) == 0
+    err = (out.cpu().double().view(n, H, d) - ref).abs()
+    assert float(err.max()) < (1e-4 if dtype == torch.float32 else 0.04), (float(err.max()), np.unravel_index(int(err.argmax()), err.shape))
+
+
+@pytest.mark.parametrize("H, G, window, page, ranges", [(4, 2, 100, 16, 1), (2, 1, 0, 64, 1), (2, 2, 0, 8, 3), (3, 3, 70, 8, 2)])
+def test_a_sink_in_the_tcgen05_attention_kernel(H, G, window, page, ranges):
+    """Heads of 128: the sink is added where a row's sum is complete: in the kernel itself, or in the merge of key ranges."""
+    from quantinfer_b200 import kernels as k
+
+    d = 128
+    lens, starts = [150, 70], [0, 45]
+    q, kp, vp, table, sink, scale, cap, ref, ctx = _attention_case(H, G, d, window, page, lens, starts, H + window)
+    n = sum(lens)
+    q0, sp, _, token_req = _entries(lens, starts)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((n, H * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    bf = torch.bfloat16
+    k.attention_prefill(_d(q.view(n, H * d).to(bf)), out, _d(kp.to(bf)), _d(vp.to(bf)), _d(table), q0, sp, _i([0, 0, 1]), _i([0, 128, 150]),
+                        H, G, d, scale, window, status, impl="tcgen05", max_kv_len=max(ctx), key_ranges=ranges, softcap=cap, sink=_d(sink))
+    assert int(status.item()) == 0
+    err = (out.cpu().double().view(n, H, d) - ref).abs()
+    assert float(err.max()) < 0.04, (float(err.max()), np.unravel_index(int(err.argmax()), err.shape))
+
+
+# ---------------------------------------------------------------- one mixer alone, in an engine of one layer
+
+
+def _one_layer(tmp_path, entry, width, dtype, page_size=8, seed=77, eps=1e-6, max_tokens=512, alpha=1.3):
+    from quantinfer_b200.engine import Engine
+
+    cfg = model(16, width, eps, alpha, 2.0, [entry])
+    w = draw_weights(cfg, seed)
+    folder = write_folder(tmp_path / f"one{dtype}{seed}", cfg, w)
+    eng = Engine.from_folder(folder, dtype=dtype, page_size=page_size, max_tokens=max_tokens, max_requests=4, use_graphs=False)
+    return eng, clean(cfg), {k: v.double() for k, v in w.items()}
+
+
+def _run(eng, inputs, cuts, rid="r"):
+    """Feeds `inputs` [T, width] through the layer's mixer in portions `cuts` for one request."""
+    from quantinfer_b200.engine import StepEntry
+
+    eng.open(rid)
+    outs, a = [], 0
+    mixer = eng.model.blocks[0].mixer
+    for n in cuts:
+        eng.cache.prepare(rid, n)
+        batch = eng.make_batch([StepEntry(rid, [0] * n, [])])
+        y = mixer.forward(inputs[a:a + n].to(DEV, eng.dtype).contiguous(), batch, eng._views[0]).float()
+        if y.dim() == 3:            # the partial sums of a projection cut along K
+            y = y.sum(dim=0)
+        outs.append(y.cpu())
+        eng.raise_on_status()
+        eng.cache.commit(rid)
+        eng.cache.check_invariants()
+        a += n
+    eng.close(rid)
+    return torch.cat(outs)
+
+
+def _portions(T, sizes):
+    out, i = [], 0
+    while sum(out) < T:
+        out.append(min(sizes[i % len(sizes)], T - sum(out)))
+        i += 1
+    return out
+
+
+CUTS = {
+    "whole": lambda T: [T],
+    "one by one": lambda T: [1] * T,
+    "portions": lambda T: _portions(T, (7, 2, 16, 3, 2, 31, 5)),
+    "prompt then decode": lambda T: [T - 20] + [1] * 20,
+}
+
+
+def _latent_ref(x, cfg, w):
+    m = cfg["layers"][0]["mixer"]
+    eps = cfg["norm"]["eps"]
+    return plain.latent_attention(x, m, w, "l0.mix.", eps, plain.latent_rows(x, m, w, "l0.mix.", eps))
+
+
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("window, stretch, dims", [(9, (3.0, 64, 8.0, 1.0), 4), (16, None, 6), (17, (8.0, 16, 2.0, 0.5), 6), (None, None, 0)])
+def test_the_latent_mixer_however_the_sequence_is_cut(tmp_path, cut, window, stretch, dims):
+    """Windows that end inside a page, at its border and one beyond, over pages of 8; half-split pairs over part of the
+    rotated part, stretched or not; sinks; the output gate. One position's shared key part is made large, so that
+    every query that sees it is dominated by it or turned from it, and none beyond the window notices."""
+    entry = latent(3, 10, 6, 7, 12, rot_dims=dims, base=300.0, scaling=stretch, window=window)
+    eng, cfg, w = _one_layer(tmp_path, entry, 24, "float32", seed=21)
+    T, far = 75, 31
+    torch.manual_seed(6)
+    x = torch.randn(T, 24)
+    x[far] *= 12.0
+    ref = _latent_ref(x.double(), cfg, w)
+    got = _run(eng, x, CUTS[cut](T))
+    err = (got.double() - ref).abs().max(dim=1).values
+    assert float(err.max()) < 1e-4 * max(1.0, float(ref.abs().max())), (int(err.argmax()), float(err.max()))
+    x2 = x.clone()
+    x2[far] /= 12.0
+    moved = (_latent_ref(x2.double(), cfg, w) - ref).abs().max(dim=1).values
+    last = far + window - 1 if window else T - 1
+    if window:
+        assert float(moved[far:last + 1].min()) > 1e-3      # the premise: it shows in every row that sees it ...
+        assert float(moved[last + 1:].max()) == 0.0         # ... and in none beyond
+    else:
+        assert float(moved[far:].median()) > 1e-3           # (among dozens of keys a row or two may give it no weight)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_key_hundreds_of_positions_back(tmp_path, dtype):
+    """No window: the first position's key part is made to dominate for the whole sequence, on the tensor-core kernel
+    (latent of 32, rotated part of 16) and on the 32-bit one; prompt portions, then single tokens over key ranges."""
+    entry = latent(4, 16, 16, 16, 32, rot_dims=16, base=10000.0)
+    eng, cfg, w = _one_layer(tmp_path, entry, 32, dtype, page_size=16, seed=23, max_tokens=1024)
+    T = 600
+    torch.manual_seed(8)
+    x = torch.randn(T, 32)
+    x[0] *= 10.0
+    xq = x.to(torch.bfloat16).double() if dtype == "bfloat16" else x.double()
+    ref = _latent_ref(xq, cfg, w)
+    got = _run(eng, x, [300, 150, 110] + [1] * 40)
+    tol = 1e-4 if dtype == "float32" else 0.06
+    assert float((got.double() - ref).abs().max()) < tol * max(1.0, float(ref.abs().max()))
+    x2 = xq.clone()
+    x2[0] /= 10.0
+    assert float((_latent_ref(x2, cfg, w) - ref)[-40:].abs().max(dim=1).values.median()) > 0.01
+
+
+def _parallel_ref(x, cfg, w):
+    return plain.parallel_mixer(x, cfg["layers"][0]["mixer"], w, "l0.mix.", cfg["norm"]["eps"])
+
+
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("window, taps, page, kv", [(9, 2, 8, 2), (16, 4, 8, 4), (17, 1, 8, 1), (None, 3, 16, 2), (64, 5, 16, 4)])
+def test_the_two_branches_however_the_sequence_is_cut(tmp_path, cut, window, taps, page, kv):
+    """Softmax branch: windows that end inside a page, at its border and one beyond; values that are the unnormed keys,
+    one of them made thirty times as large, so that the rows that see it stand out; a sink; a cap in reach. Delta
+    branch: one to five taps, value heads sharing heads of q and k, a slot whose earlier owner left a state and filter rows."""
+    entry = parallel(left(6, 3, 10, rot_dims=4, window=window, softcap=3.0, base=300.0), right(4, kv, 5, 7, taps), ranks=(5, 3))
+    eng, cfg, w = _one_layer(tmp_path, entry, 24, "float32", page_size=page, seed=25)
+    T, far = 75, 31
+    torch.manual_seed(7)
+    x = torch.randn(T, 24)
+    x[far] *= 30.0
+    _run(eng, torch.randn(40, 24) * 3.0, [40], rid="earlier")
+    ref = _parallel_ref(x.double(), cfg, w)
+    got = _run(eng, x, CUTS[cut](T))
+    err = (got.double() - ref).abs().max(dim=1).values
+    assert float(err.max()) < 1e-4 * max(1.0, float(ref.abs().max())), (int(err.argmax()), float(err.max()))
+    # the premises, on the softmax branch alone: the large value shows in every row that sees it and in none beyond
+    m = cfg["layers"][0]["mixer"]["left"]
+    a = plain.grouped_attention(x.double(), m, w, "l0.mix.left.", 1e-6)
+    x2 = x.clone()
+    x2[far] /= 30.0
+    moved = (plain.grouped_attention(x2.double(), m, w, "l0.mix.left.", 1e-6) - a).abs().max(dim=1).values
+    last = far + window - 1 if window else T - 1
+    last = min(last, T - 1)
+    assert float(moved[far:last + 1].min()) > 1e-2
+    if last + 1 < T:
+        assert float(moved[last + 1:].max()) == 0.0
+
+
+def test_the_state_of_the_delta_rule_matters(tmp_path):
+    """The premise of the tests of cuts: a change thirty positions back shows in the delta branch's output."""
+    cfg = clean(model(16, 24, 1e-6, 1.0, None, [parallel(left(2, 1, 8), right(4, 2, 5, 7, 3))]))
+    w = {k: v.double() for k, v in draw_weights(cfg, 25).items()}
+    torch.manual_seed(1)
+    x = torch.randn(60, 24).double()
+    x2 = x.clone()
+    x2[10] += 1.0
+    m = cfg["layers"][0]["mixer"]["right"]
+    d = (plain.gated_delta(x2, m, w, "l0.mix.right.", 1e-6) - plain.gated_delta(x, m, w, "l0.mix.right.", 1e-6)).abs().max(dim=1).values
+    assert float(d[40]) > 1e-3 and float(d[:10].max()) == 0.0 and float(d[12]) > 1e-3      # the filter's rows matter too
+
+
+@pytest.mark.parametrize("dk, dv, kv", [(72, 8, 2), (130, 20, 1), (16, 70, 4)])
+def test_the_delta_branch_with_wide_keys_and_values(tmp_path, dk, dv, kv):
+    entry = parallel(left(2, 2, 8, window=8), right(4, kv, dk, dv, 2), ranks=(4, 6))
+    eng, cfg, w = _one_layer(tmp_path, entry, 32, "float32", seed=27)
+    T = 50
+    torch.manual_seed(9)
+    x = torch.randn(T, 32)
+    ref = _parallel_ref(x.double(), cfg, w)
+    got = _run(eng, x, [13, 2, 1, 1, 30, 3])
+    assert float((got.double() - ref).abs().max()) < 1e-4 * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("kind", ["latent", "parallel"])
+def test_three_hundred_single_steps_in_bfloat16(tmp_path, kind):
+    """A state (and a window) carried through three hundred steps of one token stays where the whole sequence in one
+    step puts it."""
+    entry = (latent(4, 16, 16, 16, 32, rot_dims=16, window=40) if kind == "latent"
+             else parallel(left(4, 2, 16, rot_dims=8, window=24, softcap=10.0), right(2, 1, 16, 16, 4), ranks=(8, 8)))
+    eng, cfg, w = _one_layer(tmp_path, entry, 32, "bfloat16", page_size=16, seed=29, max_tokens=512)
+    T = 303
+    torch.manual_seed(10)
+    x = torch.randn(T, 32)
+    xq = x.to(torch.bfloat16).double()
+    ref = _latent_ref(xq, cfg, w) if kind == "latent" else _parallel_ref(xq, cfg, w)
+    got = _run(eng, x, [3] + [1] * (T - 3))
+    whole = _run(eng, x, [T])
+    tol = 0.08 * max(1.0, float(ref.abs().max()) / 4)
+    assert float((got.double() - ref).abs().max()) < tol and float((whole.double() - ref).abs().max()) < tol
+    assert float((got[-50:] - whole[-50:]).abs().max()) < tol
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("ff", [None, 36])
+def test_the_block_whose_norms_come_after_the_sums(tmp_path, dtype, ff):
+    """One layer as a whole through the step function in portions; the stream after the layer against the plain
+    implementation, with and without a feed-forward."""
+    from quantinfer_b200.engine import StepEntry
+
+    entry = parallel(left(2, 1, 8, rot_dims=4, window=12), right(2, 2, 6, 5, 3), ff=ff)
+    eng, cfg, w = _one_layer(tmp_path, entry, 24, dtype, seed=31, alpha=2.2)
+    toks = random_tokens(40, 16, seed=2)
+    ref = plain.forward(cfg, w, toks, keep_layers=True)[1][0]
+    taken = []
+    eng.model.tap = lambda call, resid, delta: taken.append(resid.clone().cpu())
+    eng.open("r")
+    for a, b in ((0, 9), (9, 10), (10, 12), (12, 40)):
+        eng.step([StepEntry("r", toks[a:b], [])])
+    got = torch.cat(taken)
+    assert float((got.double() - ref).abs().max()) < (2e-5 if dtype == "float32" else 0.03) * max(1.0, float(ref.abs().max()))
+
+
+# ---------------------------------------------------------------- whole models, replayed
+
+
+def _family(name, reqs, family):
+    longest = round64(max(LENGTHS[name]))
+    if family == "whole":
+        return whole_trace(reqs), longest
+    if family == "tail":
+        return tail_trace(reqs, 48), longest
+    if family == "portions":
+        return portions_trace(reqs), longest
+    steps, peak = mixed_trace(reqs, seed=5, max_live=4, max_tokens=longest + 2 * 64)
+    assert sum(round64(n) for n in LENGTHS[name]) > peak and max(len(s["entries"]) for s in steps) >= 3
+    return steps, peak
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
+def test_replay_family(models, name, dtype, family):
+    folder, cfg, w = models[name]
+    steps, max_tokens = _family(name, _requests(name), family)
+    got = run_trace_engine(folder, dtype, steps, max_tokens, PAGE_SIZES[name])
+    _compare(got, _expect(models, name), name, dtype, family)
+
+
+def test_the_cuts_agree_with_one_another_in_float32(models):
+    """What a position's logits are must not depend on how its prompt was cut or on its company in the batch."""
+    folder, cfg, w = models["P"]
+    reqs = _requests("P")
+    runs = []
+    for family in ("whole", "tail", "portions", "mixed"):
+        steps, max_tokens = _family("P", reqs, family)
+        runs.append(run_trace_engine(folder, "float32", steps, max_tokens, PAGE_SIZES["P"]))
+    for other in runs[1:]:
+        worst = max(float(np.abs(other[k] - runs[0][k]).max()) for k in runs[0])
+        assert worst <= 2e-5, worst
+
+
+def test_a_stale_state_shows(models):
+    """The premise of the replay tests: a request that takes over a slot without its state being cleared (the manager's
+    zeroing switched off, and the kernels told that the sequence goes on) gives other logits, far beyond the bound."""
+    from quantinfer_b200.engine import Engine, StepEntry
+
+    folder, cfg, w = models["P"]
+    eng = Engine.from_folder(folder, dtype="float32", page_size=8, max_tokens=256, max_requests=1)
+    a, b = random_tokens(40, cfg["vocab"], 1), random_tokens(30, cfg["vocab"], 2)
+    eng.open("a")
+    eng.step([StepEntry("a", a, [])])
+    eng.close("a")
+    eng.open("b")
+    clean_run = eng.step([StepEntry("b", b, [29])]).cpu().clone()
+    eng.close("b")
+    eng.open("a")
+    eng.step([StepEntry("a", a, [])])
+    stale = eng.cache._state_rows.clone()
+    eng.close("a")
+    eng.open("b")
+    eng.step([StepEntry("b", b[:1], [])])
+    eng.cache._state_rows.copy_(stale)             # as if the slot had not been cleared
+    dirty = eng.step([StepEntry("b", b[1:], [28])]).cpu()
+    assert float((dirty - clean_run).abs().max()) > 50 * TOL_F32
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(models, dtype):
+    """bin/trace_run as a child process, the default page size, four slots, a mixed trace in which pages and slots are
+    used again."""
+    import tempfile
+    from pathlib import Path
+
+    folder, cfg, w = models["Q"]
+    reqs = _requests("Q")
+    steps, peak = mixed_trace(reqs, seed=9, max_live=4, max_tokens=round64(max(LENGTHS["Q"])) + 128)
+    with tempfile.TemporaryDirectory() as out:
+        cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", out,
+               "--max-tokens", str(peak)]
+        r = subprocess.run(cmd, input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-3000:]
+        assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+        outputs = {}
+        for s in steps:
+            wanted = sum(len(e["want"]) for e in s["entries"])
+            if wanted:
+                outputs[s["step"]] = np.fromfile(Path(out) / f"{s['step']}.f32", dtype="<f4").reshape(wanted, cfg["vocab"])
+    _compare(collect(steps, outputs), _expect(models, "Q"), "Q", dtype, "trace_run")
+
+
+# ---------------------------------------------------------------- generation through the scheduler
+
+
+def _plain_greedy(cfg, w, prompt, n_new):
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(plain.forward(cfg, w, toks)[-1].argmax()))
+    return toks[len(prompt):]
+
+
+@pytest.mark.parametrize("name, run_ahead, graphs", [("P", True, True), ("R", False, True), ("Q", True, False)])
+def test_greedy_generation_through_the_scheduler(models, name, run_ahead, graphs):
+    """Three prompts of unequal length taken in portions of five tokens while earlier ones already decode, decode
+    steps replayed from CUDA graphs and launched ahead of the host: the plain implementation's tokens."""
+    import quantinfer_b200 as q
+    from quantinfer_b200.engine import Engine
+
+    folder, cfg, w = models[name]
+    prompts = [random_tokens(n, cfg["vocab"], seed=n) for n in (13, 1, 27)]
+    eng = Engine.from_folder(folder, dtype="float32", page_size=PAGE_SIZES[name], max_tokens=512, max_requests=4, use_graphs=graphs)
+    model_ = q.Model.from_engine(eng, max_batch_tokens=16, chunk_size=5, run_ahead=run_ahead)
+    got = model_.generate_batch(prompts, max_new_tokens=10, eos_token_id=None)
+    for p, g in zip(prompts, got):
+        assert g == _plain_greedy(cfg, w, p, 10), (name, len(p))
+    # again on the same engine: slots and pages of the first call are used again, state must start afresh
+    assert model_.generate_batch(prompts[::-1], max_new_tokens=10, eos_token_id=None) == got[::-1]
+    assert model_.generate_tokens(prompts[2], max_new_tokens=10, eos_token_id=None) == got[2]
+
+
+def test_command_line_generates_the_same_tokens(models):
+    folder, cfg, w = models["R"]
+    prompt = random_tokens(9, cfg["vocab"], seed=1)
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "quantinfer"), "generate", "--input", str(folder), "--tokens",
+                        ",".join(map(str, prompt)), "--max-new-tokens", "10", "--dtype", "float32", "--page-size", "8"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("generated_tokens=")][0]
+    assert json.loads(line.split("=", 1)[1]) == _plain_greedy(cfg, w, prompt, 10)
+
+
+def test_random_weights_from_the_command_line(tmp_path):
+    """`--random-weights` draws a model of this design from its config.json alone (the low-rank pairs' ranks are free there)."""
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(clean(CONFIGS["P"])))
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "quantinfer"), "generate", "--input", str(cfg), "--random-weights", "--tokens",
+                        "1,2,3", "--max-new-tokens", "5", "--page-size", "8"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert len(json.loads([l for l in r.stdout.splitlines() if l.startswith("generated_tokens=")][0].split("=", 1)[1])) == 5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_past_windows_and_pages(models, dtype):
+    """Three tokens of prompt, then a hundred and fifty decoded one by one with given ids: every window passes over decoded
+    tokens, pages fill and go back, the delta rule's state and filter rows are carried through every step."""
+    folder, cfg, w = models["P"]
+    toks = random_tokens(153, cfg["vocab"], seed=8)
+    steps = tail_trace({"long": toks}, 150)
+    got = run_trace_engine(folder, dtype, steps, 192, PAGE_SIZES["P"])
+    _compare(got, plain_rows(cfg, w, {"long": toks}), "P", dtype, "long decode")
