@@ -242,8 +242,48 @@ def dulotar_arithmetic(config, spec):
     return a
 
 
+def lemotar_arithmetic(config, spec):
+    """The same for a model of the Lemotar design: per layer the mixer's projections (latent attention: q, latent, the
+    per-head products, gate, out; two branches: q, k, out of the softmax branch, q, k, v, beta, the two low-rank pairs of
+    rank 16 and out of the delta rule), the gated feed-forward's three matrices, attention over the keys of the window
+    (latent attention in the form that never expands keys and values), and the delta rule's multiply-adds (seven a state
+    element and token) with the 32-bit state it reads and writes in a decode step."""
+    H, V = spec.hidden_size, spec.vocab_size
+    params = scan_flops = state_bytes = 0
+    rank = 16
+    windows, latents = [], []
+    for layer in config.layers:
+        m = layer.mixer
+        if layer.kind == "latent_attention":
+            params += H * m.heads * (m.dim + m.rot_dim) + (0 if m.kv_from is not None else H * (m.kv_rank + m.rot_dim))
+            params += m.heads * m.kv_rank * (m.dim + m.vdim) + 2 * m.heads * m.vdim * H
+            latents.append((m.heads, m.kv_rank, m.rot_dim, m.window))
+        else:
+            l, r = m.left, m.right
+            params += H * (l.heads + l.kv_heads) * l.dim + l.heads * l.dim * H
+            params += H * (2 * r.kv_heads * r.dim + r.heads * r.vdim + r.heads) + 2 * rank * H + rank * r.heads * (r.dim + r.vdim) + r.heads * r.vdim * H
+            windows.append((l.heads, l.dim, l.kv_heads, l.window))
+            scan_flops += 7.0 * r.heads * r.dim * r.vdim
+            state_bytes += 2 * 4 * (r.heads * r.dim * r.vdim + (r.conv - 1) * (2 * r.kv_heads * r.dim + r.heads * r.vdim))
+        if layer.ff is not None:
+            params += 3 * H * layer.ff
+    a = dict(L=len(config.layers), H=H, V=V, layer_params=params / len(config.layers), stored_params=params)
+    a["weight_bytes"] = 2 * (params + V * H)
+    a["kv_bytes_per_token"] = 0
+    a["kv_bytes"] = lambda ctx: (sum(2 * g * 2 * d * (min(ctx, w) if w else ctx) for _, d, g, w in windows)
+                                 + sum(2 * (R + r) * (min(ctx, w) if w else ctx) for _, R, r, w in latents))
+    a["state_bytes"] = state_bytes
+    a["gemm_flops"] = lambda T, rows_=1: 2.0 * T * params + 2.0 * H * V * rows_
+    a["attn_flops"] = lambda T: (sum(4.0 * h * d * sum(min(t + 1, w or T) for t in range(T)) for h, d, _, w in windows)
+                                 + sum(2.0 * h * (2 * R + r) * sum(min(t + 1, w or T) for t in range(T)) for h, R, r, w in latents))
+    a["scan_flops"] = lambda T: scan_flops * T
+    return a
+
+
 def model_arithmetic(config, spec):
     """Parameter counts, bytes and flops of the configuration (every matrix bf16)."""
+    if type(config).__name__ == "LemotarConfig":
+        return lemotar_arithmetic(config, spec)
     if type(config).__name__ == "KiruvikConfig":
         return kiruvik_arithmetic(config, spec)
     if type(config).__name__ == "DulotarConfig":
@@ -595,6 +635,49 @@ def compare_dulotar(args):
     return compare_kiruvik(args, "Dulotar layers beside Kiruvik layers of equal width", DULOTAR_SIZES, dulotar_entries)
 
 
+# ---- the Lemotar design beside Dulotar layers of equal width ------------------------------------------------------
+# (width, latent-attention heads of 64 + 64 with values of 128 over a latent of 256, softmax heads / kv heads of 128,
+# delta-rule heads of 64 x 128 over a quarter as many heads of q and k, gated feed-forward of three matrices): four
+# layers, latent attention, two branches, two branches, latent attention over the first layer's latent, each with its
+# feed-forward; beside them the closest existing design, Dulotar (two branches of softmax attention and a matrix-state
+# recurrence; time mixing, whose decay per key channel is the delta rule's), as two branches + dense, time mixing, time
+# mixing, two branches + dense, with feed-forwards of two matrices that hold the same weights
+LEMOTAR_SIZES = {
+    "2048": dict(width=2048, lat_heads=16, rank=256, heads=16, kv=4, dheads=16, dkv=4, ff=5504, ff2=6656, lheads=16, wheads=32),
+    "4096": dict(width=4096, lat_heads=32, rank=256, heads=32, kv=8, dheads=32, dkv=8, ff=8192, ff2=8320, lheads=32, wheads=64),
+}
+
+
+def lemotar_entries(size):
+    z = LEMOTAR_SIZES[size]
+    lat = {"heads": z["lat_heads"], "dim": 64, "rot_dim": 64, "vdim": 128, "kv_rank": z["rank"], "scale": 128 ** -0.5,
+           "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}, "mask": {"size": 4096}}
+    both = {"left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+                     "rot": {"base": 500000.0, "dims": 64}, "mask": {"size": KIRUVIK_CHUNK}},
+            "right": {"heads": z["dheads"], "kv_heads": z["dkv"], "dim": 64, "vdim": 128, "conv": 4}}
+    den = {"kind": "dense", "ff": z["ff"]}
+    new = dict(architecture="Lemotar", vocab=COMPARE_VOCAB, width=z["width"], norm={"eps": 1e-5}, postln_alpha=2.0, embedding={"scale": 1.0},
+               layers=[{"type": "latent_attention", "mixer": lat, "mlp": den}, {"type": "parallel", "mixer": both, "mlp": den},
+                       {"type": "parallel", "mixer": both, "mlp": den}, {"type": "latent_attention", "mixer": dict(lat, kv_from=0), "mlp": den}])
+    old_both = {"left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4, "softcap": 50.0,
+                         "rot": {"base": 500000.0, "dims": 64}, "mask": {"size": KIRUVIK_CHUNK}},
+                "right": {"heads": z["lheads"], "dim": 64, "vdim": 128, "decay": [1.0 - 2.0 ** -(2 + 6 * i / z["lheads"]) for i in range(z["lheads"])]},
+                "left_scale": 1.0, "right_scale": 0.5}
+    den2 = {"kind": "dense", "ff": z["ff2"]}
+    old = dict(architecture="Dulotar", vocab=COMPARE_VOCAB, width=z["width"], norm={"eps": 1e-5}, embedding={"scale": 1.0}, canon={"taps": 4},
+               layers=[{"type": "parallel", "mixer": old_both, "mlp": den2}, {"type": "wkv", "mixer": {"heads": z["wheads"], "dim": 64}, "mlp": den2},
+                       {"type": "wkv", "mixer": {"heads": z["wheads"], "dim": 64}, "mlp": den2}, {"type": "parallel", "mixer": old_both, "mlp": den2}])
+    common = dict(seed=5, prompt_len=COMPARE_PROMPT, context=4096, batch=COMPARE_BATCH, points=())
+    return (dict(common, config=new, name=f"Lemotar layers of width {size}"), dict(common, config=old, name=f"Dulotar layers of width {size}"))
+
+
+def compare_lemotar(args):
+    """Prefill and decode throughput of four Lemotar layers (latent attention, softmax attention and the gated delta rule side by
+    side, norms after the sums, gated feed-forwards) beside four Dulotar layers of the same width, and each kernel class of
+    both alone with its share of the roofline."""
+    return compare_kiruvik(args, "Lemotar layers beside Dulotar layers of equal width", LEMOTAR_SIZES, lemotar_entries)
+
+
 def compare_kiruvik(args, title="Kiruvik layers beside dense GQA (Qwen3) layers of equal width", sizes=None, entries_of=None):
     """Prefill and decode throughput of four Kiruvik layers (attention and state-space mixers, dense and routed
     feed-forwards) beside four dense GQA layers of the same width, heads and vocabulary, and each kernel class of both
@@ -930,7 +1013,7 @@ def main() -> int:
                     help="run one part only (for profiler captures of a small case)")
     ap.add_argument("--timeline", action="store_true",
                     help="build the kernels with their time stamps and print where a decode step's time goes, kernel by kernel")
-    ap.add_argument("--compare", nargs="?", const="bebuvik", default=None, choices=["bebuvik", "kiruvik", "dulotar"],
+    ap.add_argument("--compare", nargs="?", const="bebuvik", default=None, choices=["bebuvik", "kiruvik", "dulotar", "lemotar"],
                     help="instead of the headline workload: layers of another design (default: the latent-attention design) "
                          "beside dense GQA layers of equal sizes")
     ap.add_argument("--compare-sizes", default=None, help="widths to compare, with commas between them (default: all)")
@@ -959,7 +1042,7 @@ def main() -> int:
     torch.cuda.set_device(0)
     if args.compare:
         args.skip_points = args.skip_classes = True
-        run = {"kiruvik": compare_kiruvik, "dulotar": compare_dulotar, "bebuvik": compare_designs}[args.compare]
+        run = {"kiruvik": compare_kiruvik, "dulotar": compare_dulotar, "bebuvik": compare_designs, "lemotar": compare_lemotar}[args.compare]
         print(json.dumps(run(args)))
         return 0
     if args.only == "mixed":

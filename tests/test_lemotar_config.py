@@ -119,3 +119,16 @@ def test_tensors_are_drawn_with_free_ranks():
     needs = tensor_needs_of_spec(s)
     assert needs["l1.mix.right.g1"] == TensorNeed((None, 48)) and needs["l1.mix.right.g2"].drawn_shape() == (48, 16)
     assert hasattr(random_weights, "__name__")
+
+
+def test_the_comparison_of_the_bench_holds_equal_weights():
+    """`bench.py --compare lemotar`: both stacks are valid configurations of their designs and hold the same weights to 3 %."""
+    import bench
+
+    for size in bench.LEMOTAR_SIZES:
+        new, old = bench.lemotar_entries(size)
+        a, b = (bench.model_arithmetic(c, c.to_model_spec()) for c in (config_from_dict(new["config"]), config_from_dict(old["config"])))
+        assert abs(a["weight_bytes"] / b["weight_bytes"] - 1.0) < 0.03
+        needs = tensor_needs_of_spec(config_from_dict(new["config"]).to_model_spec())
+        stored = sum(math.prod(16 if d is None else d for d in n.shape) for k, n in needs.items() if len(n.shape) == 2 and ".conv" not in k and k != "embed")
+        assert abs(2 * stored / a["weight_bytes"] - 1.0) < 0.01       # the count of the arithmetic is the count of the tensors
