@@ -1344,7 +1344,7 @@ def token_shift(h, mu, state, out, token_req, q_start, start_pos, slot_ids) -> N
 
 def matrix_state_scan(mode: str, r, k, v, state, o, q_start, start_pos, slot_ids, heads: int, dk: int, dv: int, *, log_decay=None,
                       decay_bias=None, bonus=None, head_decay=None, decay_out=None, write_state: bool = True, beta=None,
-                      qk_heads: int | None = None, unit_eps: float = 1e-6, q_scale: float = 1.0) -> None:
+                      qk_heads: int | None = None, unit_eps: float = 1e-6, q_scale: float = 1.0, prepared: bool | None = None) -> None:
     """A recurrence over a matrix state S [dk, dv] a head that decays and receives k_t v_t^T with every token.
     mode "channel_decay": o_t = S_(t-1)^T r_t + (sum_i r_i bonus_i k_i) v_t, then S_t = diag(w_t) S_(t-1) + k_t v_t^T with
     w_t = exp(-exp(log_decay_t + decay_bias)) per head and key channel. mode "head_decay": r, k, v pass silu first,
@@ -1357,7 +1357,11 @@ def matrix_state_scan(mode: str, r, k, v, state, o, q_start, start_pos, slot_ids
     o_t = S_t^T r_t, with r and k [n, qk_heads dk] made unit vectors per head (x / sqrt(sum x^2 + unit_eps)), r times
     q_scale; heads / qk_heads heads share one head of r and k; beta = sigmoid of `beta` [n, heads]; w_t =
     exp(-exp(head_decay_h) softplus(log_decay_t + decay_bias)) with head_decay the logarithm of each head's rate. Entries
-    run in one piece (the recurrence's factor is not diagonal), so `decay_out` is not offered."""
+    run in one piece (the recurrence's factor is not diagonal), so `decay_out` is not offered; instead a column's key
+    channels are spread over neighbouring lanes, so that a token costs a few multiply-adds and shuffles on the way from one
+    state to the next, and a prompt of one request spreads over heads x (dv / columns a block) blocks. `prepared`: True
+    runs the two-launch form (unit vectors, decays and beta once a token, then a scan fed by asynchronous copies), False
+    the one-launch form; None: the two-launch form for steps of more than four tokens an entry."""
     if mode not in ("channel_decay", "head_decay", "delta"):
         raise KernelError(f"matrix_state_scan: unknown mode {mode!r}")
     for t, name in ((r, "r"), (k, "k"), (v, "v")):
@@ -1399,12 +1403,25 @@ def matrix_state_scan(mode: str, r, k, v, state, o, q_start, start_pos, slot_ids
         _req(decay_out, "decay_out", torch.float32, 3)
         if tuple(decay_out.shape) != (start_pos.numel(), heads, dk):
             raise KernelError("matrix_state_scan: decay_out must be [entries, heads, dk]")
-    _call("scan", "matrix_state_scan", library().qi_matrix_state_scan_ex, 2 if delta else 0 if channel else 1, _ptr(r),
-          C.c_longlong(r.stride(0)), _ptr(k), C.c_longlong(k.stride(0)), _ptr(v), C.c_longlong(v.stride(0)), _ptr(log_decay),
-          C.c_longlong(log_decay.stride(0) if (channel or delta) else 0),
+    if delta:       # a kernel of its own: a column's key channels spread over neighbouring lanes
+        # steps with prompt portions (known from the shapes alone, so that a captured step stays what it was): unit vectors,
+        # decays and beta once a token by a kernel of their own, then a scan that only moves rows
+        scratch = None
+        if prepared if prepared is not None else n > 4 * start_pos.numel():
+            lib = library()
+            lib.qi_delta_rule_scratch_floats.restype = C.c_longlong
+            scratch = torch.empty(lib.qi_delta_rule_scratch_floats(n, heads, qk_heads, dk), dtype=torch.float32, device=r.device)
+        _call("scan", "delta_rule_scan", library().qi_delta_rule_scan, _ptr(r), C.c_longlong(r.stride(0)), _ptr(k), C.c_longlong(k.stride(0)),
+              _ptr(v), C.c_longlong(v.stride(0)), _ptr(log_decay), C.c_longlong(log_decay.stride(0)), _ptr(beta), C.c_longlong(beta.stride(0)),
+              _code(r), _ptr(decay_bias), _ptr(head_decay), _ptr(state), C.c_longlong(state.stride(0)), _ptr(o), int(bool(write_state)),
+              _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), start_pos.numel(), heads, qk_heads, dk, dv, C.c_float(unit_eps),
+              C.c_float(q_scale), _ptr(scratch), n, _stream())
+        return
+    _call("scan", "matrix_state_scan", library().qi_matrix_state_scan, 0 if channel else 1, _ptr(r), C.c_longlong(r.stride(0)), _ptr(k),
+          C.c_longlong(k.stride(0)), _ptr(v), C.c_longlong(v.stride(0)), _ptr(log_decay), C.c_longlong(log_decay.stride(0) if channel else 0),
           _code(r), _ptr(decay_bias), _ptr(bonus), _ptr(head_decay), _ptr(state), C.c_longlong(state.stride(0)), _ptr(o),
           _ptr(decay_out), int(bool(write_state)), _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), start_pos.numel(), heads, dk, dv,
-          _ptr(beta), C.c_longlong(beta.stride(0) if delta else 0), qk_heads, C.c_float(unit_eps), C.c_float(q_scale), _stream())
+          _stream())
 
 
 def matrix_state_chain(seg_state, seg_decay, state, entry_seg, start_pos, slot_ids) -> None:

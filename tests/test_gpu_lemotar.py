@@ -178,9 +178,11 @@ def test_whole_projection_norms_rotation_and_values_from_keys(interleaved, H, G,
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads, qk_heads, dk, dv", [(4, 2, 6, 6), (2, 2, 32, 32), (2, 1, 40, 70), (2, 2, 100, 8), (1, 1, 130, 20), (4, 1, 16, 130)])
-def test_the_delta_rule_kernel(dtype, heads, qk_heads, dk, dv):
+@pytest.mark.parametrize("prepared", [False, True])
+def test_the_delta_rule_kernel(dtype, heads, qk_heads, dk, dv, prepared):
     """Keys of 6 to 130 numbers (padded to the next size the kernel has), more value columns than a block takes, value
-    heads that share a head of q and k, entries of 1, 2, 19 and 45 tokens, slots with and without an earlier state."""
+    heads that share a head of q and k, entries of 1, 2, 19 and 45 tokens, slots with and without an earlier state; in
+    one launch, and in the two launches of steps with prompt portions."""
     from quantinfer_b200 import kernels as k
 
     torch.manual_seed(dk + dv)
@@ -199,7 +201,8 @@ def test_the_delta_rule_kernel(dtype, heads, qk_heads, dk, dv):
     S_dev = st[:, :heads * dv * dk].unflatten(1, (heads, dv, dk))
     qs = 0.37
     k.matrix_state_scan("delta", _d(q)[:, 3:], _d(kk), _d(v)[:, :heads * dv], S_dev, o, q0, sp, slots, heads, dk, dv, log_decay=_d(lw),
-                        decay_bias=_d(dt_bias), head_decay=_d(a_log), beta=_d(bl)[:, 1:1 + heads], qk_heads=qk_heads, unit_eps=1e-6, q_scale=qs)
+                        decay_bias=_d(dt_bias), head_decay=_d(a_log), beta=_d(bl)[:, 1:1 + heads], qk_heads=qk_heads, unit_eps=1e-6, q_scale=qs,
+                        prepared=prepared)
     a = 0
     for e, ln in enumerate(lens):
         group = torch.arange(heads) // (heads // qk_heads)
