@@ -73,7 +73,7 @@ gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict_
                            int page_size, int num_pages, const int* __restrict__ q_start, const int* __restrict__ start_pos,
                            int n_entries, int nq, int nkv, int d, int dv, float scale_log2e, float softcap, float out_scale,
                            int window, int chunk, const qi::bf16* __restrict__ gate, long long ldg, const float* __restrict__ sink,
-                           int* __restrict__ status) {
+                           int n_ranges, float* __restrict__ ws_o, float* __restrict__ ws_ml, int* __restrict__ status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     constexpr int SK = DK + kPad, SV = DV + kPad;
     qi::bf16* Qs = reinterpret_cast<qi::bf16*>(smem_raw);       // [kQT][SK]
@@ -146,11 +146,17 @@ gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict_
         fill_tile_async(Vbuf + (size_t)buf * kKT * SV, SV, kKT, dv, DV, k_pages, [&](int r) { return page_row(r, v_pages, dv); });
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    const int t_first = lo_min / kKT * kKT;
-    request_tile(t_first, 0);
+    int t_first = lo_min / kKT * kKT, t_last = hi;
+    if (n_ranges > 1) {
+        // the tile's key tiles in n_ranges equal parts, one a CTA along grid.z; a merge kernel adds the parts
+        const int per = ((hi - t_first) / kKT + n_ranges) / n_ranges;
+        t_first += (int)blockIdx.z * per * kKT;
+        t_last = min(hi, t_first + per * kKT - 1);
+    }
     int buf = 0;
-    for (int t0 = t_first; t0 <= hi; t0 += kKT, buf ^= 1) {
-        if (t0 + kKT <= hi) {            // the next tile lands while this one is multiplied
+    if (t_first <= t_last) request_tile(t_first, 0);
+    for (int t0 = t_first; t0 <= t_last; t0 += kKT, buf ^= 1) {
+        if (t0 + kKT <= t_last) {        // the next tile lands while this one is multiplied
             request_tile(t0 + kKT, buf ^ 1);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
@@ -233,6 +239,27 @@ gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict_
     if (bad_page && status) atomicOr(status, qi::kStatusBadPage);
     lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
     lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    if (n_ranges > 1) {       // this part's reference, sum and accumulator as they are; the merge kernel finishes the rows
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = half ? rB : rA;
+            if (r >= rows) continue;
+            const size_t slot = ((size_t)(row0 + r) * nq + h) * n_ranges + blockIdx.z;
+            if ((lane & 3) == 0) {
+                ws_ml[slot * 2] = half ? mB : mA;
+                ws_ml[slot * 2 + 1] = half ? lB : lA;
+            }
+#pragma unroll
+            for (int n = 0; n < DV / 8; ++n) {
+                const int col = n * 8 + (lane & 3) * 2;
+                if (col < dv) {
+                    ws_o[slot * dv + col] = o[n][2 * half];
+                    ws_o[slot * dv + col + 1] = o[n][2 * half + 1];
+                }
+            }
+        }
+        return;
+    }
     if (sink) {       // one more term in the denominator, exp(sink_h), with no key and no value (m is a base-2 exponent)
         const float sb = sink[h] * 1.4426950408889634f;
         if (mA != -INFINITY) lA += exp2f(sb - mA);
@@ -259,13 +286,40 @@ gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict_
     }
 }
 
+// out[t, h, :] = sum_s o_s 2^(m_s - M) / (sum_s l_s 2^(m_s - M) + 2^(sink_h log2 e - M)), then the gate and the factor:
+// the parts of a row that the key ranges left, added in range order.
+__global__ void gated_attention_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, qi::bf16* __restrict__ out,
+                                             int nq, int dv, int n_ranges, const qi::bf16* __restrict__ gate, long long ldg,
+                                             const float* __restrict__ sink, float out_scale) {
+    qi::pdl_wait();
+    const int h = blockIdx.x;
+    const size_t t = blockIdx.y;
+    const size_t base = (t * nq + h) * n_ranges;
+    float M = -INFINITY;
+    for (int s = 0; s < n_ranges; ++s) M = fmaxf(M, ws_ml[(base + s) * 2]);
+    const float sink_term = (sink && M != -INFINITY) ? exp2f(sink[h] * 1.4426950408889634f - M) : 0.f;
+    for (int col = threadIdx.x; col < dv; col += blockDim.x) {
+        float L = sink_term, O = 0.f;
+        for (int s = 0; s < n_ranges; ++s) {
+            const float ms = ws_ml[(base + s) * 2];
+            if (ms == -INFINITY) continue;          // a part without keys
+            const float f = exp2f(ms - M);
+            L += ws_ml[(base + s) * 2 + 1] * f;
+            O += ws_o[(base + s) * dv + col] * f;
+        }
+        float v = L > 0.f ? O / L : 0.f;
+        if (gate) v = v / (1.0f + expf(-__bfloat162float(gate[t * (size_t)ldg + (size_t)h * dv + col])));
+        out[(t * nq + h) * dv + col] = __float2bfloat16_rn(v * out_scale);
+    }
+}
+
 int padded(int v) { return v <= 32 ? 32 : v <= 64 ? 64 : v <= 96 ? 96 : 128; }
 
 template <int DK, int DV>
 int launch_one(dim3 grid, cudaStream_t stream, const void* q, void* out, const void* k_pages, const void* v_pages,
                const int* block_table, int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
                int n_entries, int nq, int nkv, int d, int dv, float scale_log2e, float softcap, float out_scale, int window, int chunk,
-               const void* gate, long long ldg, const float* sink, int* status) {
+               const void* gate, long long ldg, const float* sink, int n_ranges, float* ws_o, float* ws_ml, int n_tokens, int* status) {
     const size_t smem = sizeof(qi::bf16) * ((size_t)(kQT + 2 * kKT) * (DK + kPad) + (size_t)2 * kKT * (DV + kPad));
     static bool raised = false;
     if (!raised && smem > 48 * 1024) {
@@ -274,7 +328,13 @@ int launch_one(dim3 grid, cudaStream_t stream, const void* q, void* out, const v
     }
     qi::launch(gated_attention_mma_kernel<DK, DV>, grid, dim3(kThreads), smem, stream, (const qi::bf16*)q, (qi::bf16*)out,
                (const qi::bf16*)k_pages, (const qi::bf16*)v_pages, block_table, max_blocks, page_size, num_pages, q_start, start_pos,
-               n_entries, nq, nkv, d, dv, scale_log2e, softcap, out_scale, window, chunk, (const qi::bf16*)gate, ldg, sink, status);
+               n_entries, nq, nkv, d, dv, scale_log2e, softcap, out_scale, window, chunk, (const qi::bf16*)gate, ldg, sink, n_ranges, ws_o, ws_ml, status);
+    if (n_ranges > 1) {
+        if (int rc = qi::check_launch("gated_attention_mma")) return rc;
+        qi::launch(gated_attention_merge_kernel, dim3(nq, n_tokens), dim3(128), 0, stream, (const float*)ws_o, (const float*)ws_ml,
+                   (qi::bf16*)out, nq, dv, n_ranges, (const qi::bf16*)gate, ldg, sink, out_scale);
+        return qi::check_launch("gated_attention_merge");
+    }
     return qi::check_launch("gated_attention_mma");
 }
 
@@ -288,11 +348,14 @@ extern "C" int qi_gated_attention_mma_supported(int nq, int nkv, int d, int dv) 
 // start_pos [entries]; gate (may be null) row t, head h, element i at gate[t * ldg + h * dv + i] (ldg and dv even);
 // softcap c > 0: a score s becomes c tanh(s / c) before the softmax; out_scale multiplies the result. sink (may be null):
 // float32 [nq]; the softmax's denominator of head h holds exp(sink[h]) once more.
-extern "C" int qi_gated_attention_mma_sink(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
+// n_ranges > 1 (steps of single tokens over long contexts): every query tile's keys are cut into that many ranges over
+// separate CTAs and a second kernel adds the parts; `workspace` must then hold n_tokens * nq * n_ranges * (dv + 2) floats.
+extern "C" int qi_gated_attention_mma_ranges(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
                                       int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
                                       int n_entries, int n_tokens, int nq, int nkv, int d, int dv, float scale, float softcap,
                                       float out_scale, int window, int chunk, const void* gate, long long ldg, const float* sink,
-                                      int* status, cudaStream_t stream) {
+                                      int n_ranges, float* workspace, int* status, cudaStream_t stream) {
+    QI_REQUIRE(n_ranges >= 1 && n_ranges <= 64 && (n_ranges == 1 || (workspace && n_tokens <= 65535)), "gated_attention_mma: key ranges need a workspace (1 to 64 ranges, at most 65535 tokens)");
     QI_REQUIRE(qi_gated_attention_mma_supported(nq, nkv, d, dv), "gated_attention_mma: heads %d/%d of %d/%d are not covered", nq, nkv, d, dv);
     QI_REQUIRE(n_entries >= 0 && n_tokens >= 0 && page_size > 0 && max_blocks > 0 && num_pages > 0, "gated_attention_mma: bad sizes");
     QI_REQUIRE(window >= 0 && chunk >= 0, "gated_attention_mma: window and chunk must be >= 0 (0 = none)");
@@ -300,11 +363,13 @@ extern "C" int qi_gated_attention_mma_sink(const void* q, void* out, const void*
     QI_REQUIRE(!gate || (ldg >= (long long)nq * dv && ldg % 2 == 0), "gated_attention_mma: the gate's rows are too short or odd");
     QI_REQUIRE(nq <= 65535, "gated_attention_mma: too many heads");
     if (n_tokens == 0 || n_entries == 0) return 0;
-    const dim3 grid(n_tokens / kQT + n_entries, nq);
+    const dim3 grid(n_tokens / kQT + n_entries, nq, n_ranges);
+    float* ws_o = workspace;
+    float* ws_ml = workspace ? workspace + (size_t)n_tokens * nq * n_ranges * dv : nullptr;
     const float sl = scale * 1.4426950408889634f;
 #define QI_GA(DKP, DVP)                                                                                                      \
     return launch_one<DKP, DVP>(grid, stream, q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start, \
-                                start_pos, n_entries, nq, nkv, d, dv, sl, softcap, out_scale, window, chunk, gate, ldg, sink, status)
+                                start_pos, n_entries, nq, nkv, d, dv, sl, softcap, out_scale, window, chunk, gate, ldg, sink, n_ranges, ws_o, ws_ml, n_tokens, status)
 #define QI_GA_ROW(DKP)                                   \
     switch (padded(dv)) {                                \
         case 32: QI_GA(DKP, 32);                         \
@@ -323,6 +388,12 @@ extern "C" int qi_gated_attention_mma_sink(const void* q, void* out, const void*
     return 0;
 }
 
+extern "C" int qi_gated_attention_mma_sink(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
+                                      int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
+                                      int n_entries, int n_tokens, int nq, int nkv, int d, int dv, float scale, float softcap,
+                                      float out_scale, int window, int chunk, const void* gate, long long ldg, const float* sink,
+                                      int* status, cudaStream_t stream);
+
 extern "C" int qi_gated_attention_mma(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
                                       int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
                                       int n_entries, int n_tokens, int nq, int nkv, int d, int dv, float scale, float softcap,
@@ -330,4 +401,14 @@ extern "C" int qi_gated_attention_mma(const void* q, void* out, const void* k_pa
     return qi_gated_attention_mma_sink(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start, start_pos,
                                        n_entries, n_tokens, nq, nkv, d, dv, scale, softcap, out_scale, window, chunk, gate, ldg, nullptr,
                                        status, stream);
+}
+
+extern "C" int qi_gated_attention_mma_sink(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
+                                      int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
+                                      int n_entries, int n_tokens, int nq, int nkv, int d, int dv, float scale, float softcap,
+                                      float out_scale, int window, int chunk, const void* gate, long long ldg, const float* sink,
+                                      int* status, cudaStream_t stream) {
+    return qi_gated_attention_mma_ranges(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start, start_pos,
+                                         n_entries, n_tokens, nq, nkv, d, dv, scale, softcap, out_scale, window, chunk, gate, ldg, sink, 1,
+                                         nullptr, status, stream);
 }

@@ -599,6 +599,46 @@ __global__ void normed_sum_kernel(const TA* __restrict__ a, int ka, const TB* __
         out[row + i] = s * (va(i) * ia * ga[i] + vb(i) * ib * gb[i]);
 }
 
+// The same with a row in registers: eight neighbouring coordinates a thread, every operand read once, the loads of all
+// partial sums in flight together.
+template <typename TA, typename TB>
+__global__ void __launch_bounds__(1024) normed_sum_vec_kernel(const TA* __restrict__ a, int ka, const TB* __restrict__ b, int kb, size_t part_stride,
+                                      const float* __restrict__ ga, const float* __restrict__ gb, float eps, float s,
+                                      float* __restrict__ out, int hidden) {
+    __shared__ float scratch[32];
+    qi::pdl_wait();
+    const size_t row = (size_t)blockIdx.x * hidden;
+    const int i = threadIdx.x * 8;
+    const bool active = i < hidden;
+    float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, d[8], wa[8], wb[8];
+    if (active) {
+        Vec8<float>::load(ga + i, wa);
+        Vec8<float>::load(gb + i, wb);
+#pragma unroll 4
+        for (int k = 0; k < ka; ++k) {
+            Vec8<TA>::load(a + k * part_stride + row + i, d);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] += d[j];
+        }
+#pragma unroll 4
+        for (int k = 0; k < kb; ++k) {
+            Vec8<TB>::load(b + k * part_stride + row + i, d);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] += d[j];
+        }
+    }
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { sa = fmaf(x[j], x[j], sa); sb = fmaf(y[j], y[j], sb); }
+    const float ia = 1.0f / sqrtf(qi::block_sum(sa, scratch) / (float)hidden + eps);
+    const float ib = 1.0f / sqrtf(qi::block_sum(sb, scratch) / (float)hidden + eps);
+    if (active) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = s * (x[j] * ia * wa[j] + y[j] * ib * wb[j]);
+        Vec8<float>::store(out + row + i, x);
+    }
+}
+
 template <typename TO>
 __global__ void convert_kernel(const float* __restrict__ x, TO* __restrict__ out, size_t n) {
     qi::pdl_wait();
@@ -647,6 +687,17 @@ extern "C" int qi_normed_sum(const void* a, int ka, int dtype_a, const void* b, 
                              const float* gb, float eps, float scale, float* out, int n_rows, int hidden, cudaStream_t stream) {
     QI_REQUIRE(n_rows >= 0 && hidden > 0 && ka >= 1 && kb >= 1 && eps > 0.f, "normed_sum: bad sizes");
     if (n_rows == 0) return 0;
+    if (hidden % 8 == 0 && hidden <= 8192 && (((uintptr_t)a | (uintptr_t)b | (uintptr_t)ga | (uintptr_t)gb) & 15) == 0 && ((uintptr_t)out & 31) == 0 &&
+        ((size_t)n_rows * hidden) % 8 == 0) {
+        const int threads = (hidden / 8 + 31) / 32 * 32;
+        QI_DISPATCH_DTYPE(dtype_a, TA, {
+            QI_DISPATCH_DTYPE(dtype_b, TB, {
+                qi::launch(normed_sum_vec_kernel<TA, TB>, dim3(n_rows), dim3(threads), 0, stream, (const TA*)a, ka, (const TB*)b, kb,
+                           (size_t)n_rows * hidden, ga, gb, eps, scale, out, hidden);
+            });
+        });
+        return qi::check_launch("normed_sum");
+    }
     const int threads = pick_threads(hidden);
     QI_DISPATCH_DTYPE(dtype_a, TA, {
         QI_DISPATCH_DTYPE(dtype_b, TB, {

@@ -1588,14 +1588,18 @@ def gated_attention_mma_supported(nq: int, nkv: int, d: int, dv: int) -> bool:
 
 
 def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv, scale: float, window: int, chunk: int, gate,
-                    status, impl: str | None = None, softcap: float = 0.0, out_scale: float = 1.0, sink=None) -> None:
+                    status, impl: str | None = None, softcap: float = 0.0, out_scale: float = 1.0, sink=None,
+                    key_ranges: int | None = None) -> None:
     """Attention with separate key and value sizes, an optional chunk bound and an optional output gate, by the
     kernel that fits: "mma" (bfloat16, head sizes that are multiples of 8 up to 128: flash form on the tensor
     cores, tiles found on the device from the step's arrays) or "generic" (32-bit arithmetic, any sizes). A step
     with prompt portions whose keys and values are both of size 128 goes to "tcgen05": the portions' query tiles
     to the tcgen05 flash kernel (chunk bound and gate included), the single tokens in front of them to "mma".
     `softcap` c > 0 (a score s becomes c tanh(s / c)), `out_scale` (a factor on the result) and `sink` (float32 [nq]:
-    exp(sink[h]) once more in the softmax's denominator of head h) are known to all three."""
+    exp(sink[h]) once more in the softmax's denominator of head h) are known to all three. A step of single tokens on
+    "mma" cuts every token's keys into `key_ranges` ranges over separate CTAs (None: as many as fill the device, from
+    the longest context and the window, so that a captured step serves its whole context bucket) and adds the parts
+    in a second kernel."""
     if impl is None and q.dtype == torch.bfloat16 and d == dv and not batch.all_decode and batch.tile_req.numel() and (
             gate is None or (gate.stride(0) % 8 == 0 and gate.data_ptr() % 16 == 0)) and attention_prefill_tcgen05_supported(
             nq, nkv, d, k_pages.shape[2], block_table.shape[1]):
@@ -1635,8 +1639,14 @@ def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv
         if not gate.is_cuda or gate.dtype != q.dtype or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != out.shape:
             raise KernelError("gated_attention: the gate must be [n, nq dv] in q's type with contiguous rows")
         ldg = gate.stride(0)
-    _call("attention", "gated_attention_mma", library().qi_gated_attention_mma_sink, _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages),
+    ranges, ws = 1, None
+    if getattr(batch, "all_decode", False) and n <= 65535:
+        keys = min(window or batch.max_kv_len, chunk or batch.max_kv_len, batch.max_kv_len)
+        ranges = key_ranges or max(1, min(-(-keys // 128), 296 // max(n * nq, 1), 64))
+        if ranges > 1:
+            ws = torch.empty(n * nq * ranges * (dv + 2), dtype=torch.float32, device=q.device)
+    _call("attention", "gated_attention_mma", library().qi_gated_attention_mma_ranges, _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages),
           _ptr(block_table), block_table.shape[1], k_pages.shape[2], k_pages.shape[0], _ptr(batch.q_start), _ptr(batch.start_pos),
           batch.n_requests, n, nq, nkv, d, dv, C.c_float(scale), C.c_float(softcap or 0.0), C.c_float(out_scale), int(window or 0),
-          int(chunk or 0), _ptr(gate), C.c_longlong(ldg), _ptr(sink),
+          int(chunk or 0), _ptr(gate), C.c_longlong(ldg), _ptr(sink), ranges, _ptr(ws),
           _ptr(status), _stream())

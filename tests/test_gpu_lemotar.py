@@ -107,11 +107,12 @@ def test_the_norm_after_the_sum(dtype, h, parts):
 
 
 @pytest.mark.parametrize("ka, kb", [(1, 1), (3, 1), (2, 4)])
-def test_the_sum_of_two_normed_branches(ka, kb):
+@pytest.mark.parametrize("h", [44, 64, 2048])
+def test_the_sum_of_two_normed_branches(ka, kb, h):
     from quantinfer_b200 import kernels as k
 
     torch.manual_seed(ka * 7 + kb)
-    n, h, eps, s = 6, 44, 1e-5, 0.5
+    n, eps, s = 6, 1e-5, 0.5
     a = torch.randn(ka, n, h) if ka > 1 else torch.randn(n, h).to(torch.bfloat16)
     b = torch.randn(kb, n, h) * 3.0 if kb > 1 else (torch.randn(n, h) * 3.0)
     ga, gb = 1.0 + 0.3 * torch.randn(h), 1.0 + 0.3 * torch.randn(h)
@@ -286,6 +287,29 @@ def test_a_sink_and_a_window_in_both_attention_kernels(impl, dtype, H, G, d, win
     assert int(status.item()) == 0
     err = (out.cpu().double().view(n, H, d) - ref).abs()
     assert float(err.max()) < (1e-4 if dtype == torch.float32 else 0.04), (float(err.max()), np.unravel_index(int(err.argmax()), err.shape))
+
+
+@pytest.mark.parametrize("H, G, d, window, ranges", [(4, 2, 16, 100, 3), (2, 1, 64, 0, 5), (3, 3, 40, 9, 2), (2, 2, 128, 150, 4), (6, 2, 128, 0, None)])
+def test_single_tokens_over_key_ranges(H, G, d, window, ranges):
+    """A step of single tokens at contexts of 1 to 300: each token's keys in ranges over separate CTAs (more ranges than
+    some tokens have key tiles), the parts added by the merge kernel with the sink, against the one-CTA form's reference."""
+    from types import SimpleNamespace
+    from quantinfer_b200 import kernels as k
+
+    page, lens, starts = 8, [1, 1, 1, 1, 1], [299, 0, 63, 64, 150]
+    q, kp, vp, table, sink, scale, cap, ref, ctx = _attention_case(H, G, d, window, page, lens, starts, H * d + window + 1)
+    n, B = sum(lens), len(lens)
+    q0, sp, _, token_req = _entries(lens, starts)
+    batch = SimpleNamespace(q_start=q0, start_pos=sp, n_requests=B, token_req=token_req, all_decode=True, n_lead_decode=B, positions=_i(starts),
+                            max_kv_len=max(ctx), tile_req=_i([]), tile_q0=_i([]))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((n, H * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    bf = torch.bfloat16
+    k.gated_attention(_d(q.view(n, H * d).to(bf)), out, _d(kp.to(bf)), _d(vp.to(bf)), _d(table), batch, H, G, d, d, scale, window, 0, None, status,
+                      impl="mma", softcap=cap, sink=_d(sink), key_ranges=ranges)
+    assert int(status.item()) == 0
+    err = (out.cpu().double().view(n, H, d) - ref).abs()
+    assert float(err.max()) < 0.04, (float(err.max()), np.unravel_index(int(err.argmax()), err.shape))
 
 
 @pytest.mark.parametrize("H, G, window, page, ranges", [(4, 2, 100, 16, 1), (2, 1, 0, 64, 1), (2, 2, 0, 8, 3), (3, 3, 70, 8, 2)])
