@@ -1,7 +1,8 @@
 // Recurrent mixers whose state is of fixed size and 32-bit: a gated recurrence per channel (minGRU), and
 // recurrences over a matrix state per head that decays and receives the outer product k v^T of every token
 // (the time mixing of RWKV with a decay per key channel and a bonus for the current token; lightning
-// attention with one constant decay a head). Beside them the small kernels these mixers need: the mix of a
+// attention with one constant decay a head; the gated delta rule, whose state is decayed per key channel and corrected
+// towards each token's value). Beside them the small kernels these mixers need: the mix of a
 // token's input with its predecessor's (token shift) and the weighted sum of two branches' outputs.
 //
 // All of them work on a step's packed rows: entry e owns rows q_start[e] .. q_start[e + 1] - 1, its first
@@ -13,7 +14,6 @@
 #include "common.cuh"
 
 #include <math.h>
-#include <stdlib.h>
 
 namespace {
 
@@ -1040,13 +1040,14 @@ extern "C" int qi_delta_rule_scan(const void* q, long long ldq, const void* k, l
                    (const T*)q, ldq, (const T*)k, ldk, (const T*)v, ldv, (const T*)lw, ldw, (const T*)bproj, ldb, w0, a_log, state,  \
                    state_stride, o, write_state, q_start, start_pos, slot_ids, heads, qk_heads, dk, dv, unit_eps, q_scale);         \
     } while (0)
-    static const bool four = getenv("QI_DELTA_OWN4") != nullptr;
+    // (four channels a thread where keys are short, eight else: with four everywhere the blocks of a head, twice as many,
+    // spent more on staging the same operands than the shorter sums saved: 1,032 us against 850 for 2,048 tokens of 16 heads)
     QI_DISPATCH_DTYPE(dtype, T, {
         if (dk <= 8) QI_DR(8, 4);
         else if (dk <= 16) QI_DR(16, 4);
-        else if (dk <= 32) { if (four) QI_DR(32, 4); else QI_DR(32, 8); }
-        else if (dk <= 64) { if (four) QI_DR(64, 4); else QI_DR(64, 8); }
-        else if (dk <= 128) { if (four) QI_DR(128, 4); else QI_DR(128, 8); }
+        else if (dk <= 32) QI_DR(32, 8);
+        else if (dk <= 64) QI_DR(64, 8);
+        else if (dk <= 128) QI_DR(128, 8);
         else QI_DR(256, 8);
     });
 #undef QI_DR
