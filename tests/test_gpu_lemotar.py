@@ -560,6 +560,33 @@ def test_replay_family(models, name, dtype, family):
     _compare(got, _expect(models, name), name, dtype, family)
 
 
+@pytest.mark.parametrize("dtype, family", [("bfloat16", "whole"), ("bfloat16", "mixed"), ("float32", "portions")])
+def test_sizes_of_the_tensor_core_kernels(tmp_path, dtype, family):
+    """Softmax heads of 128 (prompt portions on the tcgen05 kernel, with window, cap and sink; single tokens over key ranges),
+    a latent of 128 with a rotated part of 32, delta-rule states of 64 x 128, pages of 64, requests of several query tiles."""
+    cfg = model(300, 256, 1e-5, 1.5, 3.0, [
+        latent(4, 64, 32, 64, 128, rot_dims=32, base=10000.0, scaling=(4.0, 128, 16.0, 1.0), window=200, ff=384),
+        parallel(left(2, 1, 128, rot_dims=64, window=100, softcap=20.0), right(2, 1, 64, 128, 4), ff=384, ranks=(16, 8)),
+        latent(2, 64, 32, 128, 128, rot_dims=32, base=10000.0, scaling=(4.0, 128, 16.0, 1.0), window=300, kv_from=0)])
+    w = draw_weights(cfg, 61)
+    folder = write_folder(tmp_path / "wide", cfg, w)
+    reqs = {f"w{i}": random_tokens(n, 300, seed=90 + i) for i, n in enumerate([300, 150, 70, 200, 40])}
+    expect = plain_rows(clean(cfg), w, reqs)
+    if family == "whole":
+        steps, max_tokens = whole_trace(reqs), 320
+    elif family == "portions":
+        steps, max_tokens = portions_trace(reqs, sizes=(70, 2, 130, 3, 64, 1)), 320
+    else:
+        steps, max_tokens = mixed_trace(reqs, seed=4, max_live=4, max_tokens=320 + 256, sizes=(2, 30, 64, 129, 17), decode_tail=12)
+    got = run_trace_engine(folder, dtype, steps, max_tokens, 64)
+    errs = np.array([float(np.abs(got[k].astype(np.float64) - expect[k].astype(np.float64)).max()) for k in expect])
+    print(f"measured wide {dtype} {family}: median {np.median(errs):.3g}, worst {errs.max():.3g}")
+    if dtype == "float32":
+        assert errs.max() <= TOL_F32
+    else:
+        assert np.median(errs) < 0.12 and (errs > 0.35).mean() <= BF16_ROWS_BEYOND and errs.max() <= BF16_WORST
+
+
 def test_the_cuts_agree_with_one_another_in_float32(models):
     """What a position's logits are must not depend on how its prompt was cut or on its company in the batch."""
     folder, cfg, w = models["P"]
